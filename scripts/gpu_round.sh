@@ -29,7 +29,7 @@ if [ -z "$SKIP_NCU" ]; then
   timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none -k 'regex:k_matvec|k_attn|k_embed|k_argmax' -c 600 \
       --csv --log-file $OUT/launches.csv python scripts/ncu_token.py 3 > $OUT/ncu_launches.log 2>&1
   # layer 0 of token 2: QKV, scores, softmax+P.V, wo, gate/up, down
-  timeout 900 ncu --set full --clock-control none --import-source on -k 'regex:k_matvec|k_attn' -s 193 -c 6 \
+  timeout 900 ncu --set full --clock-control none -k 'regex:k_matvec|k_attn' -s 193 -c 6 \
       -f -o $OUT/prof_layer python scripts/ncu_token.py 2 > $OUT/ncu_full.log 2>&1
   tail -3 $OUT/ncu_full.log
   python scripts/launch_summary.py $OUT/launches.csv > $OUT/launches_summary.txt 2>&1 || true
