@@ -17,6 +17,8 @@
 #include "../../include/booster_b200.h"
 #include "gguf.hpp"
 #include "tokenizer.hpp"
+#include "safetensors.hpp"
+#include "stack.hpp"
 #include "kernels.cuh"
 #ifndef B200_TOKEN_KERNEL
 #define B200_TOKEN_KERNEL 1      // 0: build without the persistent per-token kernel (A/B: code size of the module)
@@ -236,6 +238,8 @@ struct LayerW {
 };
 
 struct b200_model {
+    // a model of the layer-stack family (config.json + model.safetensors: stack.cu); nullptr for the GGUF LLaMA path
+    b200::StackModel * stack = nullptr;
     int device = 0;
     int n_vocab = 0, n_embd = 0, n_layer = 0, n_head = 0, n_head_kv = 0, n_ff = 0, head_dim = 0, n_ctx_train = 0;
     int layer_begin = 0, layer_end = 0;
@@ -283,7 +287,40 @@ static DevMat upload_named(const gguf_file & g, const std::string & name, int64_
 }
 
 extern "C" void b200_model_free(b200_model * m);
+// Model registry, by container: a folder with config.json + model.safetensors names its design in "architecture" and is
+// built by the layer-stack family (stack.cu: Matulorn); a GGUF file names general.architecture (llama). dtype selects the
+// storage type of a folder model's matrices: "bfloat16" (default; bf16 weights, f32 accumulation) or "float32".
+extern "C" b200_model * b200_model_load_dtype(const char * path, int device, int layer_begin, int layer_end, const char * dtype) {
+    try {
+        require_gpu();
+        if (!path) throw std::runtime_error("null model path");
+        std::string dir;
+        if (!b200::is_model_dir(path, &dir)) {
+            if (dtype && dtype[0] && std::strcmp(dtype, "bfloat16") != 0) throw std::runtime_error("a GGUF model runs in its own block formats; dtype applies to folder models");
+            return b200_model_load(path, device, layer_begin, layer_end);
+        }
+        const std::string dt = dtype && dtype[0] ? dtype : "bfloat16";
+        if (dt != "bfloat16" && dt != "float32") throw std::runtime_error("dtype must be bfloat16 or float32");
+        auto m = std::make_unique<b200_model>();
+        m->device = device;
+        m->stack = b200::stack_model_load(dir, device, dt == "float32" ? b200::STACK_F32 : b200::STACK_BF16);
+        int32_t info[B200_INFO_COUNT];
+        b200::stack_model_info(m->stack, info);
+        m->n_vocab = info[B200_INFO_N_VOCAB]; m->n_embd = info[B200_INFO_N_EMBD]; m->n_layer = info[B200_INFO_N_LAYER];
+        // the family keeps its layers on one device: any requested range loads the whole model (a one-layer probe included)
+        m->layer_begin = 0; m->layer_end = m->n_layer;
+        m->weight_bytes = b200::stack_model_weight_bytes(m->stack);
+        m->tok_model = "no_vocab";
+        return m.release();
+    } catch (const std::exception & e) {
+        set_err(e.what());
+        cudaGetLastError();
+        return nullptr;
+    }
+}
+
 extern "C" b200_model * b200_model_load(const char * path, int device, int layer_begin, int layer_end) {
+    if (path && b200::is_model_dir(path, nullptr)) return b200_model_load_dtype(path, device, layer_begin, layer_end, std::getenv("BOOSTER_B200_DTYPE"));
     std::unique_ptr<b200_model> m;
     cudaStream_t st = nullptr;
     try {
@@ -410,6 +447,7 @@ extern "C" b200_model * b200_model_load(const char * path, int device, int layer
 
 extern "C" void b200_model_free(b200_model * m) {
     if (!m) return;
+    if (m->stack) { b200::stack_model_free(m->stack); delete m; return; }
     cudaSetDevice(m->device);
     for (auto & L : m->layers) {
         cudaFree(L.qkv.alloc);
@@ -422,6 +460,7 @@ extern "C" void b200_model_free(b200_model * m) {
 
 extern "C" int b200_model_info(const b200_model * m, int32_t info[B200_INFO_COUNT]) {
     if (!m) return set_err("null model");
+    if (m->stack) { b200::stack_model_info(m->stack, info); return 0; }
     std::memset(info, 0, sizeof(int32_t) * B200_INFO_COUNT);
     info[B200_INFO_N_VOCAB] = m->n_vocab; info[B200_INFO_N_EMBD] = m->n_embd; info[B200_INFO_N_LAYER] = m->n_layer;
     info[B200_INFO_N_HEAD] = m->n_head; info[B200_INFO_N_HEAD_KV] = m->n_head_kv; info[B200_INFO_N_FF] = m->n_ff;
@@ -517,6 +556,7 @@ struct TapStore { std::map<std::string, std::vector<float>> v; };
 
 struct b200_ctx {
     b200_model * m = nullptr;
+    b200::StackCtx * stack = nullptr;     // the per-sequence state of a layer-stack model (then nothing below is allocated)
     int device = 0;
     int n_ctx = 0;
     cudaStream_t st = nullptr;
@@ -607,7 +647,7 @@ struct b200_ctx {
 };
 
 extern "C" int b200_n_ctx(const b200_ctx * c) { return c ? c->n_ctx : 0; }
-extern "C" int64_t b200_kernel_launches(const b200_ctx * c) { return c ? c->launches : 0; }
+extern "C" int64_t b200_kernel_launches(const b200_ctx * c) { return !c ? 0 : c->stack ? b200::stack_ctx_launches(c->stack) : c->launches; }
 
 enum { KIND_EMBED = 0, KIND_QKV, KIND_ATTN, KIND_WO, KIND_GATEUP, KIND_DOWN, KIND_HEAD, KIND_ATTN_PV, KIND_COUNT };
 // (thread_local: up to 8 pods run doInference concurrently, each on its own OS thread — SURVEY §8b threading)
@@ -1199,6 +1239,11 @@ extern "C" b200_ctx * b200_ctx_new(b200_model * m, int n_ctx) {
         c->m = m;
         c->device = m->device;
         CU(cudaSetDevice(m->device));
+        if (m->stack) {                 // layer-stack family: cache and recurrent state live in its own context
+            c->stack = b200::stack_ctx_new(m->stack, n_ctx);
+            c->n_ctx = b200::stack_ctx_n_ctx(c->stack);
+            return c.release();
+        }
         if (n_ctx <= 0) n_ctx = m->n_ctx_train;
         if (n_ctx <= 0) throw std::runtime_error("n_ctx must be positive (the model names no llama.context_length either)");
         c->n_ctx = (n_ctx + 31) / 32 * 32;                       // GGML_PAD(n_ctx, 32): cpp/src/llama.cpp:16655
@@ -1261,6 +1306,7 @@ extern "C" b200_ctx * b200_ctx_new(b200_model * m, int n_ctx) {
 
 extern "C" void b200_ctx_free(b200_ctx * c) {
     if (!c) return;
+    if (c->stack || c->m->stack) { if (c->stack) b200::stack_ctx_free(c->stack); delete c; return; }
     cudaSetDevice(c->m->device);
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->g_logits) cudaGraphExecDestroy(c->g_logits);
@@ -1288,6 +1334,7 @@ extern "C" void b200_ctx_free(b200_ctx * c) {
 
 extern "C" void b200_kv_clear(b200_ctx * c) {
     if (!c) return;
+    if (c->stack) { try { b200::stack_ctx_clear(c->stack); } catch (const std::exception & e) { set_err(e.what()); } return; }
     // llama_kv_cache_clear (cpp/src/llama.cpp:3135-3152): every cell empty, head 0. Attention only reads cells that hold a
     // position, so the rows themselves need no clearing.
     cudaSetDevice(c->m->device);
@@ -1430,6 +1477,7 @@ static void note_positions(b200_ctx * c, int pos_end) { if (!c->cells.managed) c
 
 // llama_kv_cache_seq_rm(ctx, 0, p0, p1) (cpp/bridge.cpp:500; cpp/src/llama.cpp:3154-3206)
 extern "C" int b200_kv_seq_rm(b200_ctx * c, int p0, int p1) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -1455,6 +1503,7 @@ extern "C" int b200_kv_seq_rm(b200_ctx * c, int p0, int p1) {
 // llama_kv_cache_seq_add(ctx, 0, p0, p1, delta) (cpp/bridge.cpp:501; cpp/src/llama.cpp:3268-3314): positions move now, the K
 // rows are re-rotated by the accumulated delta at the next decode (llama_kv_cache_update)
 extern "C" int b200_kv_seq_add(b200_ctx * c, int p0, int p1, int delta) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -1488,6 +1537,7 @@ extern "C" int b200_kv_seq_add(b200_ctx * c, int p0, int p1, int delta) {
 // cells in [p0, p1) are divided by d (integer division); the K rows are re-rotated by the accumulated delta at the next decode
 // like after a seq_add. Several cells may then hold the same position; attention only compares positions.
 extern "C" int b200_kv_seq_div(b200_ctx * c, int p0, int p1, int d) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -1516,6 +1566,7 @@ extern "C" int b200_kv_seq_div(b200_ctx * c, int p0, int p1, int d) {
 // llama_kv_cache exposes through k_l / v_l (cpp/src/llama.cpp:2495-2539; V returned position-major). Tests use the pair
 // to start both sides of a parity check from the same cache at n_kv in the thousands, and to check the K-shift.
 extern "C" int b200_kv_write(b200_ctx * c, int layer, int pos0, int n, const uint16_t * k_rows, const uint16_t * v_rows) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -1533,6 +1584,7 @@ extern "C" int b200_kv_write(b200_ctx * c, int layer, int pos0, int n, const uin
     } catch (const std::exception & e) { return set_err(e.what()); }
 }
 extern "C" int b200_kv_read(b200_ctx * c, int layer, int pos0, int n, uint16_t * k_rows, uint16_t * v_rows) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -1548,8 +1600,10 @@ extern "C" int b200_kv_read(b200_ctx * c, int layer, int pos0, int n, uint16_t *
     } catch (const std::exception & e) { return set_err(e.what()); }
 }
 
-extern "C" void b200_set_taps(b200_ctx * c, int enable) { if (c) { c->taps = enable != 0; c->tapstore.v.clear(); } }
+extern "C" void b200_set_taps(b200_ctx * c, int enable) { if (c && c->stack) { b200::stack_set_taps(c->stack, enable != 0); return; } if (c) { c->taps = enable != 0; c->tapstore.v.clear(); } }
 extern "C" int64_t b200_get_tap(b200_ctx * c, const char * name, int layer, float * out, int64_t cap) {
+    // layer-stack models keep one tap, "l_out": the residual stream after every layer of the last step, [layers][tokens][width]
+    if (c && c->stack) return (name && std::strcmp(name, "l_out") == 0 && layer < 0) ? b200::stack_get_taps(c->stack, out, cap) : 0;
     if (!c || !name) return 0;
     auto it = c->tapstore.v.find(std::string(name) + "-" + std::to_string(layer));
     if (it == c->tapstore.v.end()) return 0;
@@ -1800,8 +1854,9 @@ static void prefill_batch(b200_ctx * c, const int32_t * tokens, int n, int pos0)
 // [n][n_embd] with one peer copy (the batch counterpart of b200_stage_forward's hand-off, same events); the last stage
 // leaves the logits of the chunk's last token. Returns 2 when the batched kernels cannot run this chunk (the caller then
 // feeds the tokens one by one through b200_stage_forward).
-extern "C" int b200_stage_batch_usable(b200_ctx * c, int n) { return c && n <= PB_MAX_T && prefill_batch_usable(c, n) ? 1 : 0; }
+extern "C" int b200_stage_batch_usable(b200_ctx * c, int n) { return c && !c->stack && n <= PB_MAX_T && prefill_batch_usable(c, n) ? 1 : 0; }
 extern "C" int b200_stage_forward_batch(b200_ctx * c, const int32_t * tokens, int n, int pos0, b200_ctx * prev) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c || !tokens || n <= 0) throw std::runtime_error("bad arguments");
@@ -1839,10 +1894,38 @@ extern "C" int b200_stage_forward_batch(b200_ctx * c, const int32_t * tokens, in
     } catch (const std::exception & e) { return set_err(e.what()); }
 }
 
+// b200_decode with the logits of chosen places: rows[n_rows] are ascending indices into the step's tokens and
+// logits_out receives [n_rows][n_vocab]. The GGUF path keeps one row per step (llama_batch_get_one), so there only
+// rows = {n - 1} is accepted; layer-stack models compute the head on the wanted rows of a prompt portion.
+extern "C" int b200_decode_rows(b200_ctx * c, const int32_t * tokens, int n, int pos0, const int32_t * rows, int n_rows, float * logits_out) {
+    try {
+        require_gpu();
+        if (!c || !tokens || n <= 0 || n_rows < 0 || (n_rows && !rows)) throw std::runtime_error("bad arguments");
+        if (c->stack) {
+            const double t0 = now_us();
+            static const int32_t none = 0;
+            b200::stack_decode(c->stack, tokens, n, pos0, n_rows ? rows : &none, n_rows, logits_out);
+            const double dt = now_us() - t0;
+            if (n > 1) { c->t_prompt_us += dt; c->n_prompt += n; } else { c->t_gen_us += dt; c->n_gen += 1; }
+            c->last_device_ms = b200::stack_last_device_ms(c->stack);
+            return 0;
+        }
+        if (n_rows == 0) return b200_decode(c, tokens, n, pos0, nullptr);
+        if (n_rows != 1 || rows[0] != n - 1) throw std::runtime_error("this model keeps the last row of a step only");
+        return b200_decode(c, tokens, n, pos0, logits_out);
+    } catch (const std::exception & e) {
+        return set_err(e.what());
+    }
+}
+
 extern "C" int b200_decode(b200_ctx * c, const int32_t * tokens, int n, int pos0, float * logits_out) {
     try {
         require_gpu();
         if (!c || !tokens || n <= 0) throw std::runtime_error("bad arguments");
+        if (c->stack) {
+            const int32_t last = n - 1;
+            return b200_decode_rows(c, tokens, n, pos0, &last, 1, logits_out);
+        }
         b200_model & m = *c->m;
         if (!m.has_embd() || !m.has_head()) throw std::runtime_error("b200_decode needs a single-stage model; use b200_pipeline_decode");
         if (pos0 < 0 || pos0 + n > c->n_ctx) throw std::runtime_error("positions exceed n_ctx");   // find_slot failure: llama.cpp:14690
@@ -1901,6 +1984,19 @@ extern "C" int b200_generate_greedy(b200_ctx * c, int32_t first_token, int pos0,
         require_gpu();
         if (!c || n_steps <= 0) throw std::runtime_error("bad arguments");
         b200_model & m = *c->m;
+        if (c->stack) {                 // one graph replay + device arg-max per token
+            if (!out_tokens) throw std::runtime_error("null output");
+            float ms = 0.f;
+            int32_t tok = first_token;
+            for (int i = 0; i < n_steps; i++) {
+                b200::stack_decode(c->stack, &tok, 1, pos0 + i, nullptr, 1, nullptr);
+                ms += b200::stack_last_device_ms(c->stack);
+                out_tokens[i] = tok = b200::stack_argmax(c->stack);
+            }
+            c->last_device_ms = ms;
+            c->n_gen += n_steps;
+            return 0;
+        }
         if (!m.has_embd() || !m.has_head()) throw std::runtime_error("single-stage model required; use b200_pipeline_generate_greedy");
         if (pos0 < 0 || pos0 + n_steps > c->n_ctx) throw std::runtime_error("positions exceed n_ctx");
         if (n_steps > c->out_tokens_cap) throw std::runtime_error("n_steps too large");
@@ -1949,6 +2045,11 @@ extern "C" int b200_step_greedy(b200_ctx * c, int32_t token, int pos, int32_t * 
         require_gpu();
         if (!c || !next_token) throw std::runtime_error("bad arguments");
         b200_model & m = *c->m;
+        if (c->stack) {
+            b200::stack_decode(c->stack, &token, 1, pos, nullptr, 1, nullptr);
+            *next_token = b200::stack_argmax(c->stack);
+            return 0;
+        }
         if (!m.has_embd() || !m.has_head()) throw std::runtime_error("b200_step_greedy needs a single-stage context (use b200_stage_forward for layer splits)");
         if (pos < 0 || pos >= c->n_ctx) throw std::runtime_error("position exceeds n_ctx");
         if (token < 0 || token >= m.n_vocab) throw std::runtime_error("token id out of range");
@@ -1979,12 +2080,20 @@ extern "C" int b200_step_greedy(b200_ctx * c, int32_t token, int pos, int32_t * 
     } catch (const std::exception & e) { return set_err(e.what()); }
 }
 
+extern "C" float b200_stack_time_linear(int device, int dtype, int T, int N, int K, int reps) {
+    try {
+        require_gpu();
+        if (T <= 0 || N <= 0 || K <= 0 || reps <= 0 || (dtype != 0 && dtype != 1)) throw std::runtime_error("bad arguments");
+        return b200::stack_time_linear(device, dtype, T, N, K, reps);
+    } catch (const std::exception & e) { set_err(e.what()); cudaGetLastError(); return -1.f; }
+}
 extern "C" float b200_last_device_ms(const b200_ctx * c) { return c ? c->last_device_ms : 0.f; }
 
 // One token, un-graphed, with a CUDA-event pair around every launch on the engine's own stream:
 // ms_by_kind[k] = summed device time of kind k, n_by_kind[k] = launches of that kind
 // (kinds: 0 embed, 1 qkv, 2 attention(partial+combine), 3 wo, 4 gate/up, 5 down, 6 head).
 extern "C" int b200_profile_token(b200_ctx * c, int32_t token, int pos, float ms_by_kind[8], int32_t n_by_kind[8]) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -2014,6 +2123,7 @@ extern "C" int b200_profile_token(b200_ctx * c, int32_t token, int pos, float ms
 // pair of CUDA events. ms_total / n_launches is the kernel's steady-state launch-to-launch time without the token's
 // dependency chain around it (the next launch's weight prefetch overlaps the previous one's tail, as in the token).
 extern "C" int b200_profile_kind(b200_ctx * c, int kind, int pos, int reps, float * ms_total, int32_t * n_launches) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c || kind < 0 || kind >= KIND_COUNT || reps <= 0) throw std::runtime_error("bad arguments");
@@ -2047,6 +2157,7 @@ extern "C" int b200_profile_kind(b200_ctx * c, int kind, int pos, int reps, floa
 //         k_attn_scores 0 start | 1 after wait | 2 scores written;
 //         k_attn_softmax_pv 0 start | 1 after wait | 2 score rows staged | 3 normalised | 4 P.V done.
 extern "C" int64_t b200_trace_token(b200_ctx * c, int32_t token, int pos, int reps, uint64_t * out, int64_t cap_words, int32_t * meta, int64_t cap_meta) {
+    if (c && c->stack) { set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path"); return -1; }
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -2085,6 +2196,7 @@ extern "C" int64_t b200_trace_token(b200_ctx * c, int32_t token, int pos, int re
 // 0: the persistent kernel is not in use for this context).
 extern "C" int64_t b200_trace_phases(b200_ctx * c, int32_t token, int pos, int reps, uint64_t * out, int64_t cap_words, int32_t * kinds,
                                      int64_t cap_kinds, int32_t * n_ctas) {
+    if (c && c->stack) { set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path"); return -1; }
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -2121,6 +2233,7 @@ extern "C" int b200_comm_unique_id(uint8_t id[128]) {
     try { if (!id) throw std::runtime_error("null id"); nccl_load(); NC(g_nccl.GetUniqueId(id)); return 0; } catch (const std::exception & e) { return set_err(e.what()); }
 }
 extern "C" int b200_comm_init(b200_ctx * c, int rank, int world, const uint8_t id[128]) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c || !id || world < 1 || rank < 0 || rank >= world) throw std::runtime_error("bad arguments");
@@ -2200,6 +2313,7 @@ __global__ void k_p2p_recv_token(DecodeState * st, const P2PInbox * mine, unsign
 
 // this rank's inbox as a 64-byte CUDA IPC handle (allocates it on first use)
 extern "C" int b200_p2p_handle(b200_ctx * c, uint8_t handle[64]) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -2221,6 +2335,7 @@ extern "C" int b200_p2p_handle(b200_ctx * c, uint8_t handle[64]) {
 // map the inboxes this rank writes to: rank + 1's (next_handle; ignored on the last rank) and rank 0's (first_handle; used by
 // the last rank only). After this call b200_pipeline_* hands off over NVLink stores instead of NCCL.
 extern "C" int b200_p2p_connect(b200_ctx * c, int rank, int world, const uint8_t next_handle[64], const uint8_t first_handle[64]) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c || !c->inbox) throw std::runtime_error("b200_p2p_handle must be called first");
@@ -2284,6 +2399,7 @@ static void enqueue_stage_step(b200_ctx * c, bool greedy) {
 }
 
 extern "C" int b200_pipeline_generate_greedy(b200_ctx * c, int32_t first_token, int pos0, int n_steps, int32_t * out_tokens) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c || n_steps <= 0) throw std::runtime_error("bad arguments");
@@ -2344,6 +2460,7 @@ extern "C" int b200_pipeline_generate_greedy(b200_ctx * c, int32_t first_token, 
 }
 
 extern "C" int b200_pipeline_decode(b200_ctx * c, const int32_t * tokens, int n, int pos0, float * logits_out) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c || !tokens || n <= 0) throw std::runtime_error("bad arguments");
@@ -2371,6 +2488,7 @@ extern "C" int b200_pipeline_decode(b200_ctx * c, const int32_t * tokens, int n,
 // in-process layer split: stage chain inside one process (what the Go server drives through the bridge)
 // ------------------------------------------------------------------------------------------------------------
 extern "C" int b200_stage_forward(b200_ctx * c, int32_t token, int pos, int batch_gt1, b200_ctx * prev) {
+    if (c && c->stack) return set_err("not available for a layer-stack model: this entry point belongs to the GGUF LLaMA path");
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
@@ -2411,6 +2529,7 @@ extern "C" int b200_stage_sync(b200_ctx * c) {
     try {
         require_gpu();
         if (!c) throw std::runtime_error("null context");
+        if (c->stack) { b200::stack_sync(c->stack); return 0; }
         CU(cudaSetDevice(c->m->device));
         CU(cudaStreamSynchronize(c->st));
         return 0;
@@ -2421,6 +2540,7 @@ extern "C" int b200_stage_logits(b200_ctx * c, float * logits_out) {
         require_gpu();
         if (!c || !c->m->has_head()) throw std::runtime_error("not the last stage");
         if (!logits_out) throw std::runtime_error("null output");
+        if (c->stack) { std::memcpy(logits_out, b200::stack_logits_view(c->stack), (size_t) c->m->n_vocab * 4); return 0; }
         CU(cudaSetDevice(c->m->device));
         CU(cudaMemcpyAsync(c->h_logits, c->logits, (size_t) c->m->n_vocab * 4, cudaMemcpyDeviceToHost, c->st));
         CU(cudaStreamSynchronize(c->st));
@@ -2434,6 +2554,7 @@ extern "C" float * b200_stage_logits_view(b200_ctx * c) {
     try {
         require_gpu();
         if (!c || !c->m->has_head()) throw std::runtime_error("not the last stage");
+        if (c->stack) return b200::stack_logits_view(c->stack);
         CU(cudaSetDevice(c->m->device));
         CU(cudaMemcpyAsync(c->h_logits, c->logits, (size_t) c->m->n_vocab * 4, cudaMemcpyDeviceToHost, c->st));
         CU(cudaStreamSynchronize(c->st));
@@ -2444,6 +2565,7 @@ extern "C" float * b200_stage_logits_view(b200_ctx * c) {
 // to the pinned buffer) and one synchronisation; returns the pinned buffer (see b200_stage_logits_view)
 extern "C" float * b200_decode_view(b200_ctx * c, int32_t token, int pos) {
     if (b200_decode(c, &token, 1, pos, nullptr) != 0) return nullptr;
+    if (c->stack) return b200_stage_logits_view(c);
     return c->taps ? nullptr : c->h_logits;
 }
 extern "C" int b200_stage_argmax(b200_ctx * c, int32_t * token_out) {
@@ -2451,6 +2573,7 @@ extern "C" int b200_stage_argmax(b200_ctx * c, int32_t * token_out) {
         require_gpu();
         if (!c || !c->m->has_head()) throw std::runtime_error("not the last stage");
         if (!token_out) throw std::runtime_error("null output");
+        if (c->stack) { *token_out = b200::stack_argmax(c->stack); return 0; }
         CU(cudaSetDevice(c->m->device));
         enqueue_argmax(c, 0);
         CU(cudaMemcpyAsync(&c->h_state->token, c->d_out_tokens, 4, cudaMemcpyDeviceToHost, c->st));

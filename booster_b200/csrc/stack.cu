@@ -1,0 +1,719 @@
+// stack.cu — the layer-stack model family on the B200 engine: configuration (config.json), weights (model.safetensors),
+// per-sequence state (attention cache + recurrent state), the step function for prompt portions and single tokens, and
+// the registry of designs and mixers. Kernels: stack_kernels.cuh. C-ABI dispatch: engine.cu.
+//
+// A design is a name in config.json ("architecture") mapped to a builder that turns the configuration into a list of
+// LayerSpec; a mixer is a name ("type") mapped to a loader of its tensors and a forward routine. Matulorn is the first
+// design of the family; its three mixers are registered below and can be combined in any order and size.
+#include "stack.hpp"
+#include "safetensors.hpp"
+#include "stack_kernels.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <vector>
+
+namespace b200 {
+using namespace stk;
+
+#define SCU(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) \
+    throw std::runtime_error(std::string(#call) + ": " + cudaGetErrorString(e_)); } while (0)
+
+namespace {
+
+enum MixerKind { MIX_MINGRU = 0, MIX_LATENT, MIX_DELTA };
+constexpr int CHUNK_MAX = 512;          // tokens per pass of a prompt portion (longer steps run as several passes)
+constexpr float GLU_ALPHA = 1.702f;     // the feed-forward's sigmoid slope: fixed by the design
+
+struct DMat {                            // a weight matrix [N][K] (or a batch of them) in the model's storage type
+    void * w = nullptr;
+    float * bias = nullptr;
+    int N = 0, K = 0;
+    int64_t bytes = 0;
+};
+
+struct LayerSpec {
+    int kind = 0;
+    bool has_mlp = false;
+    float * norm1 = nullptr, * norm1b = nullptr, * norm2 = nullptr, * norm2b = nullptr;
+    // minGRU
+    int width = 0;
+    DMat zxg, o;                         // z | candidate | gate stacked row-wise; o shared by all mixers
+    // latent attention
+    int H = 0, D = 0, R = 0, V = 0, rank = 0, window = 0;
+    float scale = 1.f;
+    float * cnorm = nullptr, * sink = nullptr, * rope_freq = nullptr;
+    int rope_dims = 0;
+    float rope_mag = 1.f;
+    DMat qdkv, ukT, uv;                  // q | down-projection stacked; per head: W_uk transposed [rank][D], W_uv [V][rank]
+    // gated delta rule
+    int KH = 0, taps = 0;
+    DMat proj;                           // q | k | v | beta | decay | gate stacked
+    float * wconv = nullptr, * A_log = nullptr, * dt_bias = nullptr, * dnorm = nullptr;
+    // feed-forward
+    int ff = 0;
+    float limit = 0.f;
+    DMat gateup, down;
+    // state layout (float offsets)
+    size_t off_rec = 0, n_rec = 0;       // recurrent slab: minGRU state | delta S + conv history
+    size_t cache_row = 0;                // latent attention: floats per cached position
+    int cache_index = -1;
+};
+
+}  // namespace
+
+struct StackModel {
+    int device = 0, dtype = STACK_BF16;
+    std::string design;
+    int vocab = 0, E = 0, groups = 1;
+    float eps = 1e-6f;
+    std::vector<LayerSpec> layers;
+    void * embed = nullptr;
+    float * final_norm = nullptr;
+    DMat head;
+    int64_t weight_bytes = 0;
+    std::vector<void *> allocs;
+    // buffer widths
+    int maxP = 0, maxA = 0, maxQK = 0, maxOL = 0, maxCV = 0, maxBG = 0;
+    size_t rec_floats = 0;
+    int n_caches = 0;
+};
+
+struct StepDev {                          // device image of a step's header
+    StepState st;
+    int32_t tokens[CHUNK_MAX];
+    int32_t rows[CHUNK_MAX];
+};
+
+struct StackCtx {
+    StackModel * m = nullptr;
+    int n_ctx = 0, n_past = 0, cap = 0;
+    cudaStream_t st = nullptr;
+    float * X = nullptr, * Hn = nullptr, * Y = nullptr, * P = nullptr, * A = nullptr, * QK = nullptr, * OL = nullptr, * CV = nullptr, * BG = nullptr, * O = nullptr;
+    float * rec = nullptr;                // recurrent slab
+    std::vector<float *> caches;          // per latent-attention layer: [n_ctx][rank + R]
+    StepDev * d_step = nullptr, * h_step = nullptr;
+    float * d_logits = nullptr, * h_logits = nullptr;
+    int64_t logit_rows_cap = 0;
+    float * h_last = nullptr;             // last computed row (inside h_logits)
+    int64_t d_last_row = -1;              // its row in d_logits
+    int32_t * d_arg = nullptr, * h_arg = nullptr;
+    cudaGraphExec_t g_token = nullptr;    // one token: header in -> layers -> head -> logits out
+    bool graph_failed = false;
+    int64_t n_token_launches = 0;         // kernels per replay of g_token
+    size_t attn_smem = 0;
+    bool taps = false;
+    std::vector<float> tap_data;
+    int tap_T = 0;
+    int64_t launches = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+};
+
+namespace {
+
+// ---- uploads --------------------------------------------------------------------------------------------------
+void * dev_alloc(StackModel & m, size_t bytes) {
+    void * p = nullptr;
+    SCU(cudaMalloc(&p, std::max<size_t>(bytes, 16)));
+    m.allocs.push_back(p);
+    return p;
+}
+float * up_f32(StackModel & m, const std::vector<float> & v) {
+    float * d = (float *) dev_alloc(m, v.size() * 4);
+    SCU(cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
+    return d;
+}
+uint16_t bf16_bits(float f) {             // round to nearest even (weights stored as bfloat16 convert exactly)
+    uint32_t u; std::memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t) ((u >> 16) | 0x40);
+    return (uint16_t) ((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+DMat up_mat(StackModel & m, const std::vector<float> & w, int N, int K, const std::vector<float> * bias, int batch = 1) {
+    DMat d;
+    d.N = N; d.K = K;
+    const size_t n = (size_t) batch * N * K;
+    if (w.size() != n) throw std::runtime_error("internal: matrix size mismatch");
+    if (m.dtype == STACK_F32) {
+        d.w = dev_alloc(m, n * 4);
+        SCU(cudaMemcpy(d.w, w.data(), n * 4, cudaMemcpyHostToDevice));
+        d.bytes = (int64_t) n * 4;
+    } else {
+        std::vector<uint16_t> h(n);
+        for (size_t i = 0; i < n; i++) h[i] = bf16_bits(w[i]);
+        d.w = dev_alloc(m, n * 2);
+        SCU(cudaMemcpy(d.w, h.data(), n * 2, cudaMemcpyHostToDevice));
+        d.bytes = (int64_t) n * 2;
+    }
+    if (bias) { d.bias = up_f32(m, *bias); d.bytes += (int64_t) bias->size() * 4; }
+    m.weight_bytes += d.bytes;
+    return d;
+}
+void append(std::vector<float> & a, const std::vector<float> & b) { a.insert(a.end(), b.begin(), b.end()); }
+
+int need_int(const Json & j, const char * k, int lo = 1) {
+    const int64_t v = j.integer(k);
+    if (v < lo || v > (1 << 30)) throw std::runtime_error(std::string("config: '") + k + "' is out of range");
+    return (int) v;
+}
+
+// ---- mixers: tensors '<layer>.mix.*' ----------------------------------------------------------------------------------------
+void load_mingru(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E, w = L.width = need_int(mx, "width");
+    std::vector<float> W = sf.read_f32(p + "z", {w, E}), b = sf.read_f32(p + "z.b", {w});
+    append(W, sf.read_f32(p + "x", {w, E})); append(b, sf.read_f32(p + "x.b", {w}));
+    append(W, sf.read_f32(p + "g", {w, E})); b.resize((size_t) 3 * w, 0.f);
+    L.zxg = up_mat(m, W, 3 * w, E, &b);
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, w}), E, w, nullptr);
+    L.n_rec = (size_t) w;
+    m.maxP = std::max(m.maxP, 3 * w); m.maxA = std::max(m.maxA, w);
+}
+
+void load_latent(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E;
+    const int H = L.H = need_int(mx, "heads"), D = L.D = need_int(mx, "dim"), R = L.R = need_int(mx, "rot_dim", 0);
+    const int V = L.V = need_int(mx, "vdim"), rank = L.rank = need_int(mx, "kv_rank");
+    L.scale = (float) mx.number("scale");
+    L.window = mx.has("mask") ? (int) mx.at("mask").integer("size", 0) : 0;       // 0: every earlier position
+    if (L.window < 0) throw std::runtime_error("config: mask.size must not be negative");
+    std::vector<float> W = sf.read_f32(p + "q", {H * (D + R), E});
+    append(W, sf.read_f32(p + "dkv", {rank + R, E}));
+    L.qdkv = up_mat(m, W, H * (D + R) + rank + R, E, nullptr);
+    L.cnorm = up_f32(m, sf.read_f32(p + "dkv.norm", {rank}));
+    // W_uk [H*D][rank] -> per head transposed [rank][D]: the unrotated score q_h . (W_uk,h c) = (W_uk,h^T q_h) . c
+    const std::vector<float> uk = sf.read_f32(p + "uk", {H * D, rank});
+    std::vector<float> ukT((size_t) H * rank * D);
+    for (int h = 0; h < H; h++) for (int d = 0; d < D; d++) for (int r = 0; r < rank; r++)
+        ukT[((size_t) h * rank + r) * D + d] = uk[((size_t) h * D + d) * rank + r];
+    L.ukT = up_mat(m, ukT, rank, D, nullptr, H);
+    L.uv = up_mat(m, sf.read_f32(p + "uv", {H * V, rank}), V, rank, nullptr, H);
+    L.sink = sf.find(p + "sink") ? up_f32(m, sf.read_f32(p + "sink", {H})) : nullptr;
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
+    // rotary frequencies: f_i = base^(-2i/dims), blended by YaRN when rot.scaling is given
+    L.rope_dims = 0; L.rope_mag = 1.f;
+    std::vector<float> freq(1, 0.f);
+    if (R > 0 && mx.has("rot")) {
+        const Json & rot = mx.at("rot");
+        const int dims = L.rope_dims = (int) rot.integer("dims", R);
+        if (dims < 0 || dims > R || dims % 2) throw std::runtime_error("config: rot.dims must be even and at most rot_dim");
+        const double base = rot.number("base");
+        freq.assign((size_t) std::max(dims / 2, 1), 0.f);
+        double factor = 1.0, lo = 0, hi = 0;
+        const bool yarn = rot.has("scaling");
+        if (yarn) {
+            const Json & sc = rot.at("scaling");
+            factor = sc.number("factor");
+            const double orig = sc.number("original"), fast = sc.number("fast"), slow = sc.number("slow");
+            const auto dim_of = [&](double t) { return dims * std::log(orig / (2 * M_PI * t)) / (2 * std::log(base)); };
+            lo = std::max(std::floor(dim_of(fast)), 0.0);
+            hi = std::min(std::ceil(dim_of(slow)), (double) dims - 1);
+            L.rope_mag = (float) (0.1 * std::log(factor) + 1.0);
+        }
+        for (int i = 0; i < dims / 2; i++) {
+            double f = std::pow(base, -2.0 * i / dims);
+            if (yarn) {
+                const double ramp = std::min(std::max((i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+                f = f / factor * ramp + f * (1.0 - ramp);
+            }
+            freq[(size_t) i] = (float) f;
+        }
+    }
+    L.rope_freq = up_f32(m, freq);
+    L.cache_row = (size_t) rank + R;
+    L.cache_index = m.n_caches++;
+    m.maxP = std::max(m.maxP, H * (D + R) + rank + R); m.maxA = std::max(m.maxA, H * V);
+    m.maxQK = std::max(m.maxQK, H * (rank + R)); m.maxOL = std::max(m.maxOL, H * rank);
+}
+
+void load_delta(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E;
+    const int H = L.H = need_int(mx, "heads"), KH = L.KH = (int) mx.integer("kv_heads", H), D = L.D = need_int(mx, "dim"), V = L.V = need_int(mx, "vdim");
+    const int taps = L.taps = (int) mx.integer("conv", 1);
+    if (KH < 1 || H % KH) throw std::runtime_error("config: delta heads must be a multiple of kv_heads");
+    if (taps < 1 || taps > 64) throw std::runtime_error("config: delta conv taps out of range");
+    if (D > 256) throw std::runtime_error("delta rule: dim above 256 is not supported by the recurrence kernel");
+    std::vector<float> W = sf.read_f32(p + "q", {KH * D, E}), wc = sf.read_f32(p + "q.conv", {KH * D, taps});
+    append(W, sf.read_f32(p + "k", {KH * D, E})); append(wc, sf.read_f32(p + "k.conv", {KH * D, taps}));
+    append(W, sf.read_f32(p + "v", {H * V, E}));  append(wc, sf.read_f32(p + "v.conv", {H * V, taps}));
+    append(W, sf.read_f32(p + "b", {H, E}));
+    append(W, sf.read_f32(p + "a", {H, E}));
+    append(W, sf.read_f32(p + "g", {H * V, E}));
+    const int C = 2 * KH * D + H * V, NP = C + 2 * H + H * V;
+    L.proj = up_mat(m, W, NP, E, nullptr);
+    L.wconv = up_f32(m, wc);
+    L.A_log = up_f32(m, sf.read_f32(p + "A_log", {H}));
+    L.dt_bias = up_f32(m, sf.read_f32(p + "dt_bias", {H}));
+    L.dnorm = up_f32(m, sf.read_f32(p + "norm", {V}));
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
+    L.n_rec = (size_t) H * D * V + (size_t) (taps - 1) * C;
+    m.maxP = std::max(m.maxP, NP); m.maxA = std::max(m.maxA, H * V);
+    m.maxCV = std::max(m.maxCV, C); m.maxBG = std::max(m.maxBG, 2 * H);
+}
+
+struct MixerEntry { const char * name; int kind; void (*load)(StackModel &, LayerSpec &, const Json &, const safetensors_file &, const std::string &); };
+const MixerEntry MIXERS[] = {
+    { "mingru", MIX_MINGRU, load_mingru },
+    { "latent_attention", MIX_LATENT, load_latent },
+    { "delta", MIX_DELTA, load_delta },
+};
+
+// ---- designs ----------------------------------------------------------------------------------------------------------
+// Matulorn: embed -> layers (x += norm1b(mixer(norm1 x)); x += norm2b(ff(norm2 x)) when the layer has one) -> final norm -> head
+void build_matulorn(StackModel & m, const Json & cfg, const safetensors_file & sf) {
+    m.vocab = need_int(cfg, "vocab"); m.E = need_int(cfg, "width");
+    const Json & nj = cfg.at("norm");
+    m.eps = (float) nj.number("eps");
+    m.groups = (int) nj.integer("groups", 1);
+    if (m.groups < 1 || m.E % m.groups) throw std::runtime_error("config: width must be a multiple of norm.groups");
+    const int E = m.E;
+    {
+        const std::vector<float> e = sf.read_f32("embed", {m.vocab, E});
+        DMat d = up_mat(m, e, m.vocab, E, nullptr);
+        m.embed = d.w;
+        m.weight_bytes -= d.bytes;                 // one row per token is read, not the table
+    }
+    const Json & layers = cfg.at("layers");
+    if (layers.kind != Json::Arr || layers.arr.empty()) throw std::runtime_error("config: 'layers' must be a non-empty list");
+    for (size_t i = 0; i < layers.arr.size(); i++) {
+        const Json & lj = layers.arr[i];
+        const std::string type = lj.string("type", ""), p = "l" + std::to_string(i) + ".";
+        const MixerEntry * me = nullptr;
+        for (const MixerEntry & e : MIXERS) if (type == e.name) me = &e;
+        if (!me) throw std::runtime_error("config: layer " + std::to_string(i) + " has unknown mixer type '" + type + "'");
+        m.layers.emplace_back();
+        LayerSpec & L = m.layers.back();
+        L.kind = me->kind;
+        L.norm1 = up_f32(m, sf.read_f32(p + "norm1", {E}));
+        L.norm1b = up_f32(m, sf.read_f32(p + "norm1b", {E}));
+        me->load(m, L, lj.at("mixer"), sf, p + "mix.");
+        L.off_rec = m.rec_floats;
+        m.rec_floats += (L.n_rec + 3) / 4 * 4;
+        if (lj.has("mlp")) {
+            const Json & mj = lj.at("mlp");
+            const std::string kind = mj.string("kind", "dense");
+            if (kind != "dense") throw std::runtime_error("config: feed-forward kind '" + kind + "' is not implemented (dense)");
+            L.has_mlp = true;
+            const int ff = L.ff = need_int(mj, "ff");
+            L.limit = (float) mj.number("limit");
+            L.norm2 = up_f32(m, sf.read_f32(p + "norm2", {E}));
+            L.norm2b = up_f32(m, sf.read_f32(p + "norm2b", {E}));
+            std::vector<float> W = sf.read_f32(p + "mlp.gate", {ff, E}), b = sf.read_f32(p + "mlp.gate.b", {ff});
+            append(W, sf.read_f32(p + "mlp.up", {ff, E})); append(b, sf.read_f32(p + "mlp.up.b", {ff}));
+            L.gateup = up_mat(m, W, 2 * ff, E, &b);
+            const std::vector<float> db = sf.read_f32(p + "mlp.down.b", {E});
+            L.down = up_mat(m, sf.read_f32(p + "mlp.down", {E, ff}), E, ff, &db);
+            m.maxP = std::max(m.maxP, 2 * ff); m.maxA = std::max(m.maxA, ff);
+        }
+        m.weight_bytes += (int64_t) E * 4 * (L.has_mlp ? 4 : 2);
+    }
+    m.final_norm = up_f32(m, sf.read_f32("final.norm", {E}));
+    m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
+}
+
+struct DesignEntry { const char * name; void (*build)(StackModel &, const Json &, const safetensors_file &); };
+const DesignEntry DESIGNS[] = {
+    { "Matulorn", build_matulorn },
+};
+
+// ---- launches ---------------------------------------------------------------------------------------------------------
+bool mma_enabled() {
+    static const bool on = [] { const char * e = std::getenv("BOOSTER_B200_STACK_MMA"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, int ldx, const void * W, const float * bias, float * Y, int ldy,
+               int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0) {
+    if (T <= 0 || N <= 0) return;
+    LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0};
+    const int vecw = dtype == STACK_F32 ? 4 : 8;
+    const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
+    a.vec = K % vecw == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % vecw == 0 && al16(X) && al16(W);
+    if (launches) (*launches)++;
+    if (T <= GEMV_MAX_T) {
+        const dim3 grid((unsigned) ((N + 7) / 8), 1, (unsigned) batch);
+        if (dtype == STACK_F32) k_gemv<float><<<grid, 256, 0, st>>>(a); else k_gemv<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
+    } else if (dtype == STACK_BF16 && a.vec && mma_enabled()) {
+        const dim3 grid((unsigned) ((N + MM_BN - 1) / MM_BN), (unsigned) ((T + MM_BM - 1) / MM_BM), (unsigned) batch);
+        k_gemm_bf16_mma<<<grid, 256, 0, st>>>(a);
+    } else {
+        const dim3 grid((unsigned) ((N + 63) / 64), (unsigned) ((T + 63) / 64), (unsigned) batch);
+        if (dtype == STACK_F32) k_gemm_simt<float><<<grid, 256, 0, st>>>(a); else k_gemm_simt<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
+    }
+    SCU(cudaGetLastError());
+}
+
+void linear(StackCtx * c, const float * X, int ldx, const DMat & W, float * Y, int ldy, int T, int batch = 1, long long sX = 0, long long sY = 0) {
+    linear_on(c->st, c->m->dtype, &c->launches, X, ldx, W.w, W.bias, Y, ldy, T, W.N, W.K, batch, sX, (long long) W.N * W.K, sY);
+}
+
+void norm(StackCtx * c, const float * X, int ldx, const int32_t * rows, const float * w, int n, int groups, float * Y, int ldy, int T, bool accumulate) {
+    const int threads = std::min(256, 32 * groups);
+    k_group_norm<<<T, threads, 0, c->st>>>(X, ldx, rows, w, n, groups, c->m->eps, Y, ldy, accumulate ? 1 : 0);
+    c->launches++;
+    SCU(cudaGetLastError());
+}
+
+template <int DMAX>
+void launch_delta_scan(StackCtx * c, const LayerSpec & L, int T, int C, float * S) {
+    const int threads = std::min(128, (L.V + 31) / 32 * 32);
+    const dim3 grid((unsigned) L.H, (unsigned) ((L.V + threads - 1) / threads));
+    k_delta_scan<DMAX><<<grid, threads, 0, c->st>>>(c->CV, C, c->BG, T, L.H, L.KH, L.D, L.V, S, c->O);
+}
+
+// mixers: Hn [T][E] -> Y [T][E]
+void mixer_mingru(StackCtx * c, const LayerSpec & L, int T) {
+    linear(c, c->Hn, c->m->E, L.zxg, c->P, 3 * L.width, T);
+    k_mingru_scan<<<(L.width + 127) / 128, 128, 0, c->st>>>(c->P, T, L.width, c->rec + L.off_rec, c->A);
+    c->launches++;
+    linear(c, c->A, L.width, L.o, c->Y, c->m->E, T);
+}
+
+void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
+    const int E = c->m->E, H = L.H, D = L.D, R = L.R, rank = L.rank, V = L.V, W = rank + R;
+    const int ldp = H * (D + R) + W;
+    float * cache = c->caches[(size_t) L.cache_index];
+    linear(c, c->Hn, E, L.qdkv, c->P, ldp, T);
+    const RopeArgs rope{L.rope_freq, L.rope_dims, L.rope_mag};
+    k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK);
+    // absorbed queries, one product per head: QK[t][h][0..rank) = W_uk,h^T q[t][h][0..D)
+    linear(c, c->P, ldp, L.ukT, c->QK, H * W, T, H, D + R, W);
+    k_latent_attn<<<dim3((unsigned) T, (unsigned) H), 256, c->attn_smem, c->st>>>(c->QK, cache, H, rank, R, L.window, L.scale, L.sink, &c->d_step->st, c->OL);
+    // values, one product per head: A[t][h] = W_uv,h (sum_j w_j c_j)
+    linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
+    linear(c, c->A, H * V, L.o, c->Y, E, T);
+    c->launches += 2;
+}
+
+void mixer_delta(StackCtx * c, const LayerSpec & L, int T) {
+    const int E = c->m->E, H = L.H, KH = L.KH, D = L.D, V = L.V, C = 2 * KH * D + H * V, ldp = C + 2 * H + H * V;
+    float * S = c->rec + L.off_rec, * hist = S + (size_t) H * D * V;
+    linear(c, c->Hn, E, L.proj, c->P, ldp, T);
+    k_delta_conv<<<dim3((unsigned) ((C + 127) / 128), (unsigned) T), 128, 0, c->st>>>(c->P, ldp, T, C, L.taps, L.wconv, hist, c->CV);
+    if (L.taps > 1) { k_delta_hist<<<(C + 127) / 128, 128, 0, c->st>>>(c->P, ldp, T, C, L.taps, hist); c->launches++; }
+    k_delta_gates<<<T, 128, 0, c->st>>>(c->CV, C, c->P, ldp, H, KH, D, V, L.A_log, L.dt_bias, c->BG);
+    if (D <= 32) launch_delta_scan<32>(c, L, T, C, S);
+    else if (D <= 64) launch_delta_scan<64>(c, L, T, C, S);
+    else if (D <= 128) launch_delta_scan<128>(c, L, T, C, S);
+    else launch_delta_scan<256>(c, L, T, C, S);
+    k_delta_out<<<T, 128, 0, c->st>>>(c->O, c->P, ldp, C + 2 * H, H, V, L.dnorm, c->m->eps, c->A);
+    c->launches += 4;
+    linear(c, c->A, H * V, L.o, c->Y, E, T);
+}
+
+void tap_layer(StackCtx * c, size_t li, int T) {
+    const size_t E = (size_t) c->m->E, n = (size_t) T * E;
+    SCU(cudaMemcpyAsync(c->tap_data.data() + li * n, c->X, n * 4, cudaMemcpyDeviceToHost, c->st));
+}
+
+// the layers over the T tokens whose header (positions, ids) is already on the device
+void enqueue_layers(StackCtx * c, int T) {
+    StackModel & m = *c->m;
+    const int E = m.E;
+    if (m.dtype == STACK_F32) k_embed_rows<float><<<T, 128, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, c->X);
+    else k_embed_rows<__nv_bfloat16><<<T, 128, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, c->X);
+    c->launches++;
+    for (size_t li = 0; li < m.layers.size(); li++) {
+        const LayerSpec & L = m.layers[li];
+        norm(c, c->X, E, nullptr, L.norm1, E, m.groups, c->Hn, E, T, false);
+        switch (L.kind) {
+            case MIX_MINGRU: mixer_mingru(c, L, T); break;
+            case MIX_LATENT: mixer_latent(c, L, T); break;
+            default:         mixer_delta(c, L, T); break;
+        }
+        norm(c, c->Y, E, nullptr, L.norm1b, E, m.groups, c->X, E, T, true);
+        if (L.has_mlp) {
+            norm(c, c->X, E, nullptr, L.norm2, E, m.groups, c->Hn, E, T, false);
+            linear(c, c->Hn, E, L.gateup, c->P, 2 * L.ff, T);
+            const size_t n = (size_t) T * L.ff;
+            k_clamped_glu<<<(unsigned) ((n + 255) / 256), 256, 0, c->st>>>(c->P, T, L.ff, L.limit, GLU_ALPHA, c->A);
+            c->launches++;
+            linear(c, c->A, L.ff, L.down, c->Y, E, T);
+            norm(c, c->Y, E, nullptr, L.norm2b, E, m.groups, c->X, E, T, true);
+        }
+        if (c->taps) tap_layer(c, li, T);
+    }
+    SCU(cudaGetLastError());
+}
+
+// final norm + head on n_rows rows of the pass (row indices in d_step->rows) -> d_logits[row_off ..]
+void enqueue_head(StackCtx * c, int n_rows, int64_t row_off) {
+    StackModel & m = *c->m;
+    norm(c, c->X, m.E, c->d_step->rows, m.final_norm, m.E, m.groups, c->Hn, m.E, n_rows, false);
+    linear(c, c->Hn, m.E, m.head, c->d_logits + row_off * m.vocab, m.vocab, n_rows);
+}
+
+void ensure_logit_rows(StackCtx * c, int64_t rows) {
+    if (rows <= c->logit_rows_cap) return;
+    SCU(cudaStreamSynchronize(c->st));
+    const int64_t cap = std::max<int64_t>(rows, 16);
+    float * d = nullptr, * h = nullptr;
+    SCU(cudaMalloc(&d, (size_t) cap * c->m->vocab * 4));
+    if (cudaMallocHost(&h, (size_t) cap * c->m->vocab * 4) != cudaSuccess) { cudaFree(d); throw std::runtime_error("out of pinned host memory for the logits"); }
+    cudaFree(c->d_logits);
+    cudaFreeHost(c->h_logits);
+    c->d_logits = d; c->h_logits = h; c->logit_rows_cap = cap;
+    c->h_last = nullptr; c->d_last_row = -1;
+    if (c->g_token) { cudaGraphExecDestroy(c->g_token); c->g_token = nullptr; }      // it holds the old addresses
+}
+
+bool graph_enabled() {
+    static const bool on = [] { const char * e = std::getenv("BOOSTER_B200_STACK_GRAPH"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+// one token: header in, layers, head, logits out — the body of the replayed graph and of its un-captured twin
+void enqueue_token_step(StackCtx * c) {
+    SCU(cudaMemcpyAsync(c->d_step, c->h_step, sizeof(StepState) + sizeof(int32_t), cudaMemcpyHostToDevice, c->st));
+    SCU(cudaMemsetAsync(c->d_step->rows, 0, sizeof(int32_t), c->st));      // the wanted row is the token itself (a prompt pass leaves its own rows here)
+    enqueue_layers(c, 1);
+    enqueue_head(c, 1, 0);
+    SCU(cudaMemcpyAsync(c->h_logits, c->d_logits, (size_t) c->m->vocab * 4, cudaMemcpyDeviceToHost, c->st));
+}
+
+}  // namespace
+
+// ---- public ------------------------------------------------------------------------------------------------------------
+bool stack_knows(const std::string & architecture) {
+    for (const DesignEntry & d : DESIGNS) if (architecture == d.name) return true;
+    return false;
+}
+
+void stack_model_free(StackModel * m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    for (void * p : m->allocs) cudaFree(p);
+    delete m;
+}
+
+StackModel * stack_model_load(const std::string & dir, int device, int dtype) {
+    const Json cfg = json_parse_file(dir + "/config.json");
+    const std::string arch = cfg.string("architecture", "");
+    const DesignEntry * de = nullptr;
+    for (const DesignEntry & d : DESIGNS) if (arch == d.name) de = &d;
+    if (!de) throw std::runtime_error("unsupported architecture '" + arch + "' in " + dir + "/config.json");
+    safetensors_file sf;
+    sf.open(dir + "/model.safetensors");
+    std::unique_ptr<StackModel> m(new StackModel());
+    m->device = device; m->dtype = dtype; m->design = arch;
+    SCU(cudaSetDevice(device));
+    try {
+        de->build(*m, cfg, sf);
+    } catch (...) {
+        stack_model_free(m.release());
+        cudaGetLastError();
+        throw;
+    }
+    return m.release();
+}
+
+void stack_model_info(const StackModel * m, int32_t info[16]) {
+    std::memset(info, 0, sizeof(int32_t) * 16);
+    info[0] = m->vocab; info[1] = m->E; info[2] = (int32_t) m->layers.size();
+    for (const LayerSpec & L : m->layers) {
+        if (L.H && !info[3]) { info[3] = L.H; info[4] = L.KH ? L.KH : 1; info[6] = L.D + L.R; }
+        if (L.has_mlp && !info[5]) info[5] = L.ff;
+    }
+    info[8] = 0; info[9] = (int32_t) m->layers.size(); info[10] = m->dtype == STACK_F32 ? 0 : 32;   // ggml file types: 0 all F32, 32 BF16
+}
+int64_t stack_model_weight_bytes(const StackModel * m) { return m->weight_bytes; }
+int stack_model_device(const StackModel * m) { return m->device; }
+int stack_model_n_vocab(const StackModel * m) { return m->vocab; }
+
+void stack_ctx_free(StackCtx * c) {
+    if (!c) return;
+    cudaSetDevice(c->m->device);
+    if (c->st) cudaStreamSynchronize(c->st);
+    if (c->g_token) cudaGraphExecDestroy(c->g_token);
+    for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
+    for (float * p : c->caches) cudaFree(p);
+    cudaFree(c->d_step); cudaFree(c->d_arg);
+    cudaFreeHost(c->h_step); cudaFreeHost(c->h_logits); cudaFreeHost(c->h_arg);
+    if (c->ev0) { cudaEventDestroy(c->ev0); cudaEventDestroy(c->ev1); }
+    if (c->st) cudaStreamDestroy(c->st);
+    delete c;
+}
+
+StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
+    if (n_ctx <= 0) throw std::runtime_error("n_ctx must be positive (this model names no trained context length)");
+    std::unique_ptr<StackCtx> c(new StackCtx());
+    c->m = m; c->n_ctx = n_ctx; c->cap = std::min(n_ctx, CHUNK_MAX);
+    SCU(cudaSetDevice(m->device));
+    try {
+        SCU(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
+        const size_t cap = (size_t) c->cap;
+        const auto fl = [&](float ** p, size_t n) { SCU(cudaMalloc(p, std::max<size_t>(n, 4) * 4)); };
+        fl(&c->X, cap * m->E); fl(&c->Hn, cap * m->E); fl(&c->Y, cap * m->E);
+        fl(&c->P, cap * m->maxP); fl(&c->A, cap * m->maxA); fl(&c->QK, cap * m->maxQK); fl(&c->OL, cap * m->maxOL);
+        fl(&c->CV, cap * m->maxCV); fl(&c->BG, cap * m->maxBG); fl(&c->O, cap * m->maxA);
+        fl(&c->rec, m->rec_floats);
+        c->caches.assign((size_t) m->n_caches, nullptr);
+        size_t smem = 0;
+        for (const LayerSpec & L : m->layers) {
+            if (L.kind != MIX_LATENT) continue;
+            fl(&c->caches[(size_t) L.cache_index], (size_t) n_ctx * L.cache_row);
+            const size_t keys = (size_t) (L.window > 0 ? std::min(L.window, n_ctx) : n_ctx);
+            smem = std::max(smem, (L.cache_row + 16 + 256 + keys) * 4);
+        }
+        if (smem > 227 * 1024) throw std::runtime_error("latent attention: the window (or an unmasked context) of " + std::to_string((smem / 4)) +
+                                                        " scores exceeds one block's shared memory; use a smaller n_ctx");
+        c->attn_smem = smem;
+        if (smem > 48 * 1024) SCU(cudaFuncSetAttribute(k_latent_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        SCU(cudaMalloc(&c->d_step, sizeof(StepDev)));
+        SCU(cudaMemsetAsync(c->d_step, 0, sizeof(StepDev), c->st));
+        SCU(cudaMallocHost(&c->h_step, sizeof(StepDev)));
+        std::memset(c->h_step, 0, sizeof(StepDev));
+        SCU(cudaMalloc(&c->d_arg, 4));
+        SCU(cudaMallocHost(&c->h_arg, 4));
+        SCU(cudaEventCreate(&c->ev0)); SCU(cudaEventCreate(&c->ev1));
+        ensure_logit_rows(c.get(), 16);
+        SCU(cudaMemsetAsync(c->rec, 0, std::max<size_t>(m->rec_floats, 4) * 4, c->st));
+        SCU(cudaStreamSynchronize(c->st));
+    } catch (...) {
+        stack_ctx_free(c.release());
+        cudaGetLastError();
+        throw;
+    }
+    return c.release();
+}
+
+int stack_ctx_n_ctx(const StackCtx * c) { return c->n_ctx; }
+int stack_ctx_n_past(const StackCtx * c) { return c->n_past; }
+int64_t stack_ctx_launches(const StackCtx * c) { return c->launches; }
+float stack_last_device_ms(const StackCtx * c) { return c->last_ms; }
+
+void stack_ctx_clear(StackCtx * c) {
+    SCU(cudaSetDevice(c->m->device));
+    // recurrent state back to zero; cached positions need no clearing: a sequence only reads positions it wrote
+    SCU(cudaMemsetAsync(c->rec, 0, std::max<size_t>(c->m->rec_floats, 4) * 4, c->st));
+    SCU(cudaStreamSynchronize(c->st));
+    c->n_past = 0;
+    c->h_last = nullptr; c->d_last_row = -1;
+}
+
+void stack_set_taps(StackCtx * c, bool on) { c->taps = on; c->tap_data.clear(); c->tap_T = 0; }
+int64_t stack_get_taps(StackCtx * c, float * out, int64_t cap) {
+    const int64_t n = (int64_t) c->tap_data.size();
+    if (out) std::memcpy(out, c->tap_data.data(), (size_t) std::min(n, cap) * 4);
+    return n;
+}
+
+void stack_decode(StackCtx * c, const int32_t * tokens, int n, int pos0, const int32_t * rows, int n_rows, float * logits_out) {
+    StackModel & m = *c->m;
+    if (!tokens || n <= 0) throw std::runtime_error("empty step");
+    if (pos0 != c->n_past) throw std::runtime_error("this model carries recurrent state: a step must continue the sequence at position " +
+                                                    std::to_string(c->n_past) + " (got " + std::to_string(pos0) + "); clear the context to start a new one");
+    if ((int64_t) pos0 + n > c->n_ctx) throw std::runtime_error("the step exceeds the context of " + std::to_string(c->n_ctx) + " positions");
+    for (int i = 0; i < n; i++) if (tokens[i] < 0 || tokens[i] >= m.vocab) throw std::runtime_error("token id " + std::to_string(tokens[i]) + " is outside the vocabulary");
+    const int32_t last_row = n - 1;
+    if (!rows) { rows = &last_row; n_rows = 1; }
+    for (int i = 0; i < n_rows; i++) if (rows[i] < 0 || rows[i] >= n || (i && rows[i] <= rows[i - 1])) throw std::runtime_error("wanted rows must be ascending indices into the step");
+    SCU(cudaSetDevice(m.device));
+    ensure_logit_rows(c, std::max(n_rows, 1));
+    SCU(cudaEventRecord(c->ev0, c->st));
+    if (n == 1 && n_rows == 1 && !c->taps && graph_enabled() && !c->graph_failed) {
+        c->h_step->st.pos0 = pos0; c->h_step->st.n_tokens = 1; c->h_step->tokens[0] = tokens[0];
+        if (!c->g_token) {
+            SCU(cudaStreamSynchronize(c->st));
+            const int64_t before = c->launches;
+            cudaGraph_t g = nullptr;
+            bool ok = cudaStreamBeginCapture(c->st, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+            if (ok) {
+                try { enqueue_token_step(c); } catch (...) { ok = false; }
+                if (cudaStreamEndCapture(c->st, &g) != cudaSuccess) ok = false;
+            }
+            if (ok && cudaGraphInstantiate(&c->g_token, g, 0) != cudaSuccess) { ok = false; c->g_token = nullptr; }
+            if (g) cudaGraphDestroy(g);
+            c->n_token_launches = c->launches - before;
+            c->launches = before;
+            if (!ok) { cudaGetLastError(); c->graph_failed = true; }
+        }
+        if (c->g_token) {
+            SCU(cudaGraphLaunch(c->g_token, c->st));
+            c->launches += c->n_token_launches;
+        } else {
+            enqueue_token_step(c);
+        }
+        SCU(cudaEventRecord(c->ev1, c->st));
+        SCU(cudaStreamSynchronize(c->st));
+        c->d_last_row = 0; c->h_last = c->h_logits;
+    } else {
+        if (c->taps) { c->tap_data.assign(m.layers.size() * (size_t) n * m.E, 0.f); c->tap_T = n; if (n > c->cap) throw std::runtime_error("taps need a step of at most one pass"); }
+        int64_t row_off = 0;
+        int ri = 0;
+        for (int i0 = 0; i0 < n; i0 += c->cap) {
+            const int T = std::min(c->cap, n - i0);
+            SCU(cudaStreamSynchronize(c->st));              // the pinned header is free again
+            c->h_step->st.pos0 = pos0 + i0; c->h_step->st.n_tokens = T;
+            std::memcpy(c->h_step->tokens, tokens + i0, (size_t) T * 4);
+            int nr = 0;
+            while (ri < n_rows && rows[ri] < i0 + T) c->h_step->rows[nr++] = rows[ri++] - i0;
+            SCU(cudaMemcpyAsync(c->d_step, c->h_step, sizeof(StepState) + (size_t) T * 4, cudaMemcpyHostToDevice, c->st));
+            if (nr) SCU(cudaMemcpyAsync(c->d_step->rows, c->h_step->rows, (size_t) nr * 4, cudaMemcpyHostToDevice, c->st));
+            enqueue_layers(c, T);
+            if (nr) { enqueue_head(c, nr, row_off); row_off += nr; }
+        }
+        if (row_off) SCU(cudaMemcpyAsync(c->h_logits, c->d_logits, (size_t) row_off * m.vocab * 4, cudaMemcpyDeviceToHost, c->st));
+        SCU(cudaEventRecord(c->ev1, c->st));
+        SCU(cudaStreamSynchronize(c->st));
+        if (row_off) { c->d_last_row = row_off - 1; c->h_last = c->h_logits + (size_t) (row_off - 1) * m.vocab; }
+    }
+    cudaEventElapsedTime(&c->last_ms, c->ev0, c->ev1);
+    c->n_past = pos0 + n;
+    if (logits_out && n_rows > 0) std::memcpy(logits_out, c->h_logits, (size_t) n_rows * m.vocab * 4);
+}
+
+void stack_sync(StackCtx * c) {
+    SCU(cudaSetDevice(c->m->device));
+    SCU(cudaStreamSynchronize(c->st));
+}
+
+float * stack_logits_view(StackCtx * c) {
+    if (!c->h_last) throw std::runtime_error("no logits yet: the last step asked for none");
+    return c->h_last;
+}
+
+int32_t stack_argmax(StackCtx * c) {
+    if (c->d_last_row < 0) throw std::runtime_error("no logits yet: the last step asked for none");
+    SCU(cudaSetDevice(c->m->device));
+    k_argmax_row<<<1, 1024, 0, c->st>>>(c->d_logits + (size_t) c->d_last_row * c->m->vocab, c->m->vocab, c->d_arg);
+    c->launches++;
+    SCU(cudaMemcpyAsync(c->h_arg, c->d_arg, 4, cudaMemcpyDeviceToHost, c->st));
+    SCU(cudaStreamSynchronize(c->st));
+    return *c->h_arg;
+}
+
+float stack_time_linear(int device, int dtype, int T, int N, int K, int reps) {
+    SCU(cudaSetDevice(device));
+    float * X = nullptr, * Y = nullptr; void * W = nullptr;
+    cudaStream_t st = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    float ms = 0.f;
+    // several distinct weight matrices so that a repetition does not find its operand in L2
+    const size_t wbytes = (size_t) N * K * (dtype == STACK_F32 ? 4 : 2);
+    const int copies = (int) std::min<size_t>(8, std::max<size_t>(1, ((size_t) 256 << 20) / std::max<size_t>(wbytes, 1) + 1));
+    try {
+        SCU(cudaMalloc(&X, (size_t) T * K * 4)); SCU(cudaMalloc(&Y, (size_t) T * N * 4)); SCU(cudaMalloc(&W, wbytes * copies));
+        SCU(cudaMemset(X, 0, (size_t) T * K * 4)); SCU(cudaMemset(W, 0, wbytes * copies));
+        SCU(cudaStreamCreate(&st)); SCU(cudaEventCreate(&e0)); SCU(cudaEventCreate(&e1));
+        for (int i = 0; i < 3; i++) linear_on(st, dtype, nullptr, X, K, (char *) W + wbytes * (size_t) (i % copies), nullptr, Y, N, T, N, K);
+        SCU(cudaStreamSynchronize(st));
+        SCU(cudaEventRecord(e0, st));
+        for (int i = 0; i < reps; i++) linear_on(st, dtype, nullptr, X, K, (char *) W + wbytes * (size_t) (i % copies), nullptr, Y, N, T, N, K);
+        SCU(cudaEventRecord(e1, st));
+        SCU(cudaStreamSynchronize(st));
+        cudaEventElapsedTime(&ms, e0, e1);
+    } catch (...) {
+        cudaFree(X); cudaFree(Y); cudaFree(W);
+        if (st) cudaStreamDestroy(st);
+        throw;
+    }
+    cudaFree(X); cudaFree(Y); cudaFree(W);
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaStreamDestroy(st);
+    return ms / (float) std::max(reps, 1);
+}
+
+}  // namespace b200

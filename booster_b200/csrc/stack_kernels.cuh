@@ -1,0 +1,554 @@
+// stack_kernels.cuh — CUDA kernels (sm_100a) of the layer-stack models: a residual stream that passes a configurable
+// list of layers, each one mixer (minGRU recurrence | latent attention with a sliding window and a soft-max sink |
+// gated delta rule) and an optional clamped gated feed-forward, with grouped RMS norms before and after every
+// sub-layer. Every size and constant is a kernel argument; nothing is specialised for one model.
+//
+// Precision: the residual stream, norms, positions and angles, attention scores and weights, recurrent states and
+// everything that enters a recurrence are float32. Matrix products take float32 activations and weights in the
+// model's storage type WT (bfloat16 or float32) and accumulate in float32; the tensor-core product (k_gemm_bf16_mma)
+// rounds its activation operand to bfloat16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+namespace stk {
+
+__device__ __forceinline__ float wf(const float * p, size_t i) { return p[i]; }
+__device__ __forceinline__ float wf(const __nv_bfloat16 * p, size_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// what a step works on: written by the host (or by a memcpy node of the replayed decode graph) before the launches
+struct StepState {
+    int32_t pos0;       // position of the step's first token within its sequence
+    int32_t n_tokens;
+};
+
+// ---- embedding: X[t] = embed[token[t]] ----------------------------------------------------------------------
+template <typename WT>
+__global__ void k_embed_rows(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, float * __restrict__ X) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : tok >= n_vocab ? n_vocab - 1 : tok;      // ids are validated on the host; never read outside the table
+    for (int i = threadIdx.x; i < E; i += blockDim.x) X[(size_t) t * E + i] = wf(embed, (size_t) tok * E + i);
+}
+
+// ---- RMS norm in `groups` equal consecutive parts; eps inside the root ----------------------------------------------
+// one block per row, one warp per group (round robin). rows != nullptr gathers input rows (the head's wanted rows).
+// accumulate == 0: Y[row] = norm(X[row]) * w;  accumulate == 1: Y[row] += norm(X[row]) * w  (the residual sum)
+__global__ void k_group_norm(const float * __restrict__ X, int ldx, const int32_t * __restrict__ rows, const float * __restrict__ w,
+                             int n, int groups, float eps, float * __restrict__ Y, int ldy, int accumulate) {
+    const int row = blockIdx.x, src = rows ? rows[row] : row;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int gs = n / groups;
+    const float * x = X + (size_t) src * ldx;
+    float * y = Y + (size_t) row * ldy;
+    for (int g = warp; g < groups; g += nw) {
+        const int b = g * gs;
+        float ss = 0.f;
+        for (int i = lane; i < gs; i += 32) { const float v = x[b + i]; ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float) gs + eps);
+        for (int i = lane; i < gs; i += 32) {
+            const float v = x[b + i] * r * w[b + i];
+            y[b + i] = accumulate ? y[b + i] + v : v;
+        }
+    }
+}
+
+// ---- matrix products: Y[t][n] = sum_k X[t][k] * W[n][k] (+ bias[n]); W row-major [N][K] -------------------------------
+// blockIdx.z runs over a batch of independent products (per-head matrices) with element strides sX / sW / sY.
+struct LinArgs {
+    const float * X; const void * W; const float * bias; float * Y;
+    int T, N, K, ldx, ldy;
+    long long sX, sW, sY;
+    int vec;            // 1: K, ldx and all bases allow 16-byte loads
+};
+
+constexpr int GEMV_MAX_T = 4;
+// decode and very short portions: one warp per output row, the row of W streamed once with 16-byte loads
+template <typename WT>
+__global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (n >= a.N) return;
+    const WT * w = reinterpret_cast<const WT *>(a.W) + (size_t) blockIdx.z * a.sW + (size_t) n * a.K;
+    const float * x = a.X + (size_t) blockIdx.z * a.sX;
+    float acc[GEMV_MAX_T];
+#pragma unroll
+    for (int t = 0; t < GEMV_MAX_T; t++) acc[t] = 0.f;
+    constexpr int VEC = 16 / (int) sizeof(WT);
+    if (a.vec) {
+        for (int k = lane * VEC; k < a.K; k += 32 * VEC) {
+            float wv[VEC];
+            if constexpr (sizeof(WT) == 2) {
+                const uint4 u = *reinterpret_cast<const uint4 *>(w + k);
+                const uint32_t uu[4] = { u.x, u.y, u.z, u.w };
+#pragma unroll
+                for (int i = 0; i < 4; i++) { wv[2 * i] = __uint_as_float(uu[i] << 16); wv[2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u); }
+            } else {
+                const float4 f = *reinterpret_cast<const float4 *>(w + k);
+                wv[0] = f.x; wv[1] = f.y; wv[2] = f.z; wv[3] = f.w;
+            }
+#pragma unroll
+            for (int t = 0; t < GEMV_MAX_T; t++) {
+                if (t < a.T) {
+                    const float * xt = x + (size_t) t * a.ldx + k;
+#pragma unroll
+                    for (int i = 0; i < VEC; i += 4) {
+                        const float4 xv = *reinterpret_cast<const float4 *>(xt + i);
+                        acc[t] = fmaf(wv[i], xv.x, acc[t]); acc[t] = fmaf(wv[i + 1], xv.y, acc[t]);
+                        acc[t] = fmaf(wv[i + 2], xv.z, acc[t]); acc[t] = fmaf(wv[i + 3], xv.w, acc[t]);
+                    }
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < a.K; k += 32) {
+            const float wv = wf(w, k);
+#pragma unroll
+            for (int t = 0; t < GEMV_MAX_T; t++) if (t < a.T) acc[t] = fmaf(wv, x[(size_t) t * a.ldx + k], acc[t]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < GEMV_MAX_T; t++) {
+        if (t < a.T) {
+            const float s = warp_sum(acc[t]);
+            if (lane == 0) a.Y[(size_t) blockIdx.z * a.sY + (size_t) t * a.ldy + n] = s + (a.bias ? a.bias[n] : 0.f);
+        }
+    }
+}
+
+// prompt portions in true float32 (and every shape the tensor-core kernel does not take): 64 x 64 x 16 tiles on the CUDA
+// cores, 256 threads with 4 x 4 outputs each
+template <typename WT>
+__global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
+    __shared__ float Xs[16][64 + 4];
+    __shared__ float Ws[16][64 + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const float * X = a.X + (size_t) blockIdx.z * a.sX;
+    const WT * W = reinterpret_cast<const WT *>(a.W) + (size_t) blockIdx.z * a.sW;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;          // this thread stages 4 consecutive k of row lr
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < a.K; k0 += 16) {
+        {
+            const int m = m0 + lr;
+            float v[4] = { 0.f, 0.f, 0.f, 0.f };
+            if (m < a.T) {
+                const float * p = X + (size_t) m * a.ldx + k0 + lk;
+                if (a.vec && k0 + lk + 3 < a.K) { const float4 f = *reinterpret_cast<const float4 *>(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+                else for (int i = 0; i < 4; i++) if (k0 + lk + i < a.K) v[i] = p[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) Xs[lk + i][lr] = v[i];
+        }
+        {
+            const int n = n0 + lr;
+            float v[4] = { 0.f, 0.f, 0.f, 0.f };
+            if (n < a.N) {
+                const size_t o = (size_t) n * a.K + k0 + lk;
+                for (int i = 0; i < 4; i++) if (k0 + lk + i < a.K) v[i] = wf(W, o + i);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) Ws[lk + i][lr] = v[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const float4 xv = *reinterpret_cast<const float4 *>(&Xs[k][ty * 4]);
+            const float4 wv = *reinterpret_cast<const float4 *>(&Ws[k][tx * 4]);
+            const float xa[4] = { xv.x, xv.y, xv.z, xv.w }, wa[4] = { wv.x, wv.y, wv.z, wv.w };
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float * Y = a.Y + (size_t) blockIdx.z * a.sY;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= a.T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j] + (a.bias ? a.bias[n] : 0.f);
+        }
+    }
+}
+
+// prompt portions with bfloat16 weights on the tensor cores: mma.sync m16n8k16 (bf16 x bf16 -> f32), CTA tile 128 (tokens)
+// x 128 (rows of W) x 32, 8 warps of 64 x 32, operands staged through registers into padded shared memory (the float32
+// activations are rounded to bfloat16 on the way), double-buffered. Needs K % 8 == 0 and 16-byte aligned rows (a.vec).
+constexpr int MM_BM = 128, MM_BN = 128, MM_BK = 32, MM_LD = MM_BK + 8;     // row stride 80 B: conflict-free ldmatrix
+__device__ __forceinline__ uint32_t smem_addr(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+__global__ void __launch_bounds__(256) k_gemm_bf16_mma(const LinArgs a) {
+    __shared__ __align__(16) __nv_bfloat16 As[2][MM_BM][MM_LD];
+    __shared__ __align__(16) __nv_bfloat16 Bs[2][MM_BN][MM_LD];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+    const int m0 = blockIdx.y * MM_BM, n0 = blockIdx.x * MM_BN;
+    const float * X = a.X + (size_t) blockIdx.z * a.sX;
+    const __nv_bfloat16 * W = reinterpret_cast<const __nv_bfloat16 *>(a.W) + (size_t) blockIdx.z * a.sW;
+    // staging: 128 rows x 32 k per operand; thread -> (row = tid / 2 [+ 0], 16 consecutive k starting at (tid & 1) * 16)
+    const int sr = tid >> 1, sk = (tid & 1) * 16;
+    float4 xa[4]; uint4 wb[2];
+    const auto fetch = [&](int k0) {
+        const int m = m0 + sr, n = n0 + sr;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int k = k0 + sk + 4 * i;
+            xa[i] = (m < a.T && k < a.K) ? *reinterpret_cast<const float4 *>(X + (size_t) m * a.ldx + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int k = k0 + sk + 8 * i;
+            wb[i] = (n < a.N && k < a.K) ? *reinterpret_cast<const uint4 *>(W + (size_t) n * a.K + k) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    const auto stash = [&](int buf) {
+        uint4 p0, p1;
+        p0.x = pack_bf16(xa[0].x, xa[0].y); p0.y = pack_bf16(xa[0].z, xa[0].w); p0.z = pack_bf16(xa[1].x, xa[1].y); p0.w = pack_bf16(xa[1].z, xa[1].w);
+        p1.x = pack_bf16(xa[2].x, xa[2].y); p1.y = pack_bf16(xa[2].z, xa[2].w); p1.z = pack_bf16(xa[3].x, xa[3].y); p1.w = pack_bf16(xa[3].z, xa[3].w);
+        *reinterpret_cast<uint4 *>(&As[buf][sr][sk]) = p0;
+        *reinterpret_cast<uint4 *>(&As[buf][sr][sk + 8]) = p1;
+        *reinterpret_cast<uint4 *>(&Bs[buf][sr][sk]) = wb[0];
+        *reinterpret_cast<uint4 *>(&Bs[buf][sr][sk + 8]) = wb[1];
+    };
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f;
+    const int nk = (a.K + MM_BK - 1) / MM_BK;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (int kt = 0; kt < nk; kt++) {
+        const int buf = kt & 1;
+        if (kt + 1 < nk) fetch((kt + 1) * MM_BK);
+#pragma unroll
+        for (int ks = 0; ks < MM_BK; ks += 16) {
+            uint32_t af[4][4], bf[2][4];
+#pragma unroll
+            for (int i = 0; i < 4; i++)      // A fragment of rows wm + 16 i ..: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+                ldsm_x4(af[i], smem_addr(&As[buf][wm + 16 * i + (lane & 15)][ks + (lane >> 4) * 8]));
+#pragma unroll
+            for (int j = 0; j < 2; j++)      // B: two n-tiles of 8 per ldmatrix.x4: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+                ldsm_x4(bf[j], smem_addr(&Bs[buf][wn + 16 * j + (lane & 7) + ((lane >> 4) << 3)][ks + ((lane >> 3) & 1) * 8]));
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) mma_bf16(acc[i][j], af[i], bf[j >> 1][(j & 1) * 2], bf[j >> 1][(j & 1) * 2 + 1]);
+        }
+        if (kt + 1 < nk) stash(buf ^ 1);
+        __syncthreads();
+    }
+    float * Y = a.Y + (size_t) blockIdx.z * a.sY;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int m = m0 + wm + 16 * i + (lane >> 2) + (e >> 1) * 8;
+                const int n = n0 + wn + 8 * j + (lane & 3) * 2 + (e & 1);
+                if (m < a.T && n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j][e] + (a.bias ? a.bias[n] : 0.f);
+            }
+}
+
+// ---- minGRU: S_t = (1 - z) S_(t-1) + z * cand, gates from the current token only ----------------------------------------
+// P[t] = [ z pre-activation | candidate pre-activation u | output-gate pre-activation ] (3 * width, biases included);
+// cand = u + 1/2 for u >= 0, sigmoid(u) below. A[t] = S_t * silu(gate). One thread per channel walks the portion in order.
+__global__ void k_mingru_scan(const float * __restrict__ P, int T, int width, float * __restrict__ state, float * __restrict__ A) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    float s = state[c];
+    const int ld = 3 * width;
+    for (int t = 0; t < T; t++) {
+        const float * p = P + (size_t) t * ld;
+        const float z = sigmoidf_(p[c]), u = p[width + c];
+        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+        s = (1.0f - z) * s + z * cand;
+        A[(size_t) t * width + c] = s * siluf_(p[2 * width + c]);
+    }
+    state[c] = s;
+}
+
+// ---- rotary positions, 'rotate half' pairing (i, i + dims/2) on the first `dims` entries of a vector -------------------------
+struct RopeArgs {
+    const float * freq;   // [dims / 2] frequencies after any YaRN blend (host-built)
+    int dims;
+    float mag;            // factor on cos and sin (YaRN: 0.1 ln(factor) + 1; else 1)
+};
+__device__ __forceinline__ void rope_pair(const RopeArgs & r, int pos, int i, float u, float v, float & ou, float & ov) {
+    const float ang = (float) pos * r.freq[i];
+    const float c = cosf(ang) * r.mag, s = sinf(ang) * r.mag;
+    ou = u * c - v * s;
+    ov = v * c + u * s;
+}
+
+// ---- latent attention, step 1: cache row + rotated query parts -------------------------------------------------------------
+// P[t] = [ q: H x (D + R) | down-projection: rank + R ]. Per token: latent c = RMS norm of the first `rank` entries of the
+// down-projection (plain weight), the last R entries are the rotated key part all heads share. The cache row of position p is
+// [ c | rotated key part ] (rank + R floats): nothing else of a key or value is kept. The query row of head h is
+// QK[t][h] = [ absorbed query (written by the per-head product q_unrotated . W_uk) | rotated query part ].
+__global__ void k_latent_prep(const float * __restrict__ P, int ldp, int H, int D, int R, int rank, const float * __restrict__ cnorm, float eps,
+                              RopeArgs rope, const StepState * __restrict__ st, float * __restrict__ cache, float * __restrict__ QK) {
+    const int t = blockIdx.x, pos = st->pos0 + t;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float * p = P + (size_t) t * ldp;
+    const float * dkv = p + (size_t) H * (D + R);
+    float * row = cache + (size_t) pos * (rank + R);
+    const int half = rope.dims / 2;
+    if (warp == 0) {
+        float ss = 0.f;
+        for (int i = lane; i < rank; i += 32) ss = fmaf(dkv[i], dkv[i], ss);
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float) rank + eps);
+        for (int i = lane; i < rank; i += 32) row[i] = dkv[i] * r * cnorm[i];
+    }
+    // rotated vectors: index H is the shared key part, 0..H-1 the heads' query parts
+    for (int v = warp; v <= H; v += nw) {
+        const float * src = v == H ? dkv + rank : p + (size_t) v * (D + R) + D;
+        float * dst = v == H ? row + rank : QK + ((size_t) t * H + v) * (rank + R) + rank;
+        for (int i = lane; i < R; i += 32) {
+            if (i < half) { float a, b; rope_pair(rope, pos, i, src[i], src[i + half], a, b); dst[i] = a; dst[i + half] = b; }
+            else if (i >= rope.dims) dst[i] = src[i];
+        }
+    }
+}
+
+// ---- latent attention, step 2: scores over the window, soft-max with a sink, weighted sum of the cached latents -------------------
+// One block per (token, head). Keys j with 0 <= p - j < window (window <= 0: every earlier position). The score of key j is
+// (QK[t][h] . cache[j]) * scale over all rank + R entries: the absorbed query against the latent plus the rotated parts. The
+// denominator also holds exp(sink[h]), which has no key and no value. OL[t][h] = sum_j w_j c_j (rank entries); the per-head
+// value matrix is applied afterwards (W_uv (sum_j w_j c_j) = sum_j w_j v_j).
+__global__ void __launch_bounds__(256) k_latent_attn(const float * __restrict__ QK, const float * __restrict__ cache, int H, int rank, int R, int window,
+                                                     float scale, const float * __restrict__ sink, const StepState * __restrict__ st, float * __restrict__ OL) {
+    extern __shared__ float sm[];
+    const int t = blockIdx.x, h = blockIdx.y, pos = st->pos0 + t;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int W = rank + R;
+    const int j0 = window > 0 ? max(0, pos - window + 1) : 0;
+    const int nk = pos - j0 + 1;
+    float * q = sm;                      // [W]
+    float * red = sm + W;                // [16]
+    float * part = red + 16;             // [256] partial sums of the weighted sum
+    float * s = part + 256;              // [nk]
+    const float * qrow = QK + ((size_t) t * H + h) * W;
+    for (int i = tid; i < W; i += 256) q[i] = qrow[i];
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int j = warp; j < nk; j += 8) {
+        const float * c = cache + (size_t) (j0 + j) * W;
+        float a = 0.f;
+        for (int i = lane; i < W; i += 32) a = fmaf(q[i], c[i], a);
+        a = warp_sum(a) * scale;
+        if (lane == 0) s[j] = a;
+        mx = fmaxf(mx, a);
+    }
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    const float snk = sink ? sink[h] : -INFINITY;
+    mx = snk;
+    for (int i = 0; i < 8; i++) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int j = tid; j < nk; j += 256) { const float e = expf(s[j] - mx); s[j] = e; sum += e; }
+    sum = warp_sum(sum);
+    if (lane == 0) red[8 + warp] = sum;
+    __syncthreads();
+    float den = sink ? expf(snk - mx) : 0.f;
+    for (int i = 0; i < 8; i++) den += red[8 + i];
+    const float inv = 1.0f / den;
+    // weighted sum: `lanes_r` threads across the latent entries, 256 / lanes_r groups across the keys
+    const int lanes_r = min(256, (rank + 31) / 32 * 32), ng = 256 / lanes_r;
+    const int g = tid / lanes_r, r0 = tid % lanes_r;
+    float * out = OL + ((size_t) t * H + h) * rank;
+    for (int rb = 0; rb < rank; rb += lanes_r) {
+        const int r = rb + r0;
+        float acc = 0.f;
+        if (g < ng && r < rank)
+            for (int j = g; j < nk; j += ng) acc = fmaf(s[j], cache[(size_t) (j0 + j) * W + r], acc);
+        if (ng == 1) { if (r < rank) out[r] = acc * inv; continue; }
+        if (g < ng) part[g * lanes_r + r0] = acc;
+        __syncthreads();
+        if (g == 0 && r < rank) {
+            float a = 0.f;
+            for (int i = 0; i < ng; i++) a += part[i * lanes_r + r0];
+            out[r] = a * inv;
+        }
+        __syncthreads();
+    }
+}
+
+// ---- gated delta rule --------------------------------------------------------------------------------------------------
+// P[t] = [ q: KH x D | k: KH x D | v: H x V | beta logit: H | decay input: H | output-gate pre-activation: H x V ].
+// Step 1: short causal convolution over time per channel of q | k | v (taps weights, the last one the current token's, no
+// bias), then silu. hist holds the taps - 1 inputs before the portion: it is part of the sequence's state.
+__global__ void k_delta_conv(const float * __restrict__ P, int ldp, int T, int C, int taps, const float * __restrict__ wconv,
+                             const float * __restrict__ hist, float * __restrict__ CV) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (c >= C) return;
+    float y = 0.f;
+    for (int k = 0; k < taps; k++) {
+        const int tau = t - (taps - 1) + k;
+        const float in = tau >= 0 ? P[(size_t) tau * ldp + c] : hist[(size_t) (taps - 1 + tau) * C + c];
+        y = fmaf(wconv[(size_t) c * taps + k], in, y);
+    }
+    CV[(size_t) t * C + c] = siluf_(y);
+}
+// afterwards: the history becomes the last taps - 1 inputs of (history ++ portion)
+__global__ void k_delta_hist(const float * __restrict__ P, int ldp, int T, int C, int taps, float * __restrict__ hist) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    for (int i = 0; i < taps - 1; i++) {          // ascending: entry i reads old entries at T + i > i only
+        const int f = T + i;                       // index into (history ++ portion)
+        hist[(size_t) i * C + c] = f < taps - 1 ? hist[(size_t) f * C + c] : P[(size_t) (f - (taps - 1)) * ldp + c];
+    }
+}
+// Step 2, per token: q and k become unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q is also scaled by D^(-1/2);
+// beta = sigmoid(beta logit); decay g = exp(-exp(A_log) * softplus(decay input + dt_bias)). BG[t] = [ beta: H | g: H ].
+__global__ void k_delta_gates(float * __restrict__ CV, int C, const float * __restrict__ P, int ldp, int H, int KH, int D, int V,
+                              const float * __restrict__ A_log, const float * __restrict__ dt_bias, float * __restrict__ BG) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float * cv = CV + (size_t) t * C;
+    for (int v = warp; v < 2 * KH; v += nw) {     // q heads, then k heads
+        float * x = cv + (size_t) v * D;
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) ss = fmaf(x[i], x[i], ss);
+        ss = warp_sum(ss);
+        float r = 1.0f / sqrtf(ss + 1e-6f);
+        if (v < KH) r *= 1.0f / sqrtf((float) D);
+        for (int i = lane; i < D; i += 32) x[i] *= r;
+    }
+    const float * p = P + (size_t) t * ldp + 2 * KH * D + H * V;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        BG[(size_t) t * 2 * H + h] = sigmoidf_(p[h]);
+        BG[(size_t) t * 2 * H + H + h] = expf(-expf(A_log[h]) * softplusf_(p[H + h] + dt_bias[h]));
+    }
+}
+// Step 3, the recurrence per head, in this order: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q — the read-out
+// sees the current token's write. S is [D][V] per head in float32; one thread owns one column of S (D registers) and walks
+// the portion token by token; head h reads q / k head h / (H / KH). DMAX >= D is the register tile (rows beyond D stay zero).
+template <int DMAX>
+__global__ void __launch_bounds__(128) k_delta_scan(const float * __restrict__ CV, int C, const float * __restrict__ BG, int T, int H, int KH, int D, int V,
+                                                    float * __restrict__ S, float * __restrict__ O) {
+    constexpr int TT = 8;
+    __shared__ float ks[TT][DMAX], qs[TT][DMAX];
+    const int h = blockIdx.x, col = blockIdx.y * blockDim.x + threadIdx.x, kh = h / (H / KH);
+    const bool live = col < V;
+    float s[DMAX];
+    float * Sh = S + (size_t) h * D * V;
+#pragma unroll
+    for (int d = 0; d < DMAX; d++) s[d] = (live && d < D) ? Sh[(size_t) d * V + col] : 0.f;
+    for (int t0 = 0; t0 < T; t0 += TT) {
+        const int nt = min(TT, T - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * DMAX; i += blockDim.x) {
+            const int tt = i / DMAX, d = i % DMAX;
+            const float * cv = CV + (size_t) (t0 + tt) * C;
+            qs[tt][d] = d < D ? cv[(size_t) kh * D + d] : 0.f;
+            ks[tt][d] = d < D ? cv[(size_t) (KH + kh) * D + d] : 0.f;
+        }
+        __syncthreads();
+        if (!live) continue;
+        for (int tt = 0; tt < nt; tt++) {
+            const int t = t0 + tt;
+            const float beta = BG[(size_t) t * 2 * H + h], g = BG[(size_t) t * 2 * H + H + h];
+            const float v = CV[(size_t) t * C + (size_t) 2 * KH * D + (size_t) h * V + col];
+            float dot = 0.f;
+#pragma unroll
+            for (int d = 0; d < DMAX; d++) { s[d] *= g; dot = fmaf(s[d], ks[tt][d], dot); }
+            const float u = beta * (v - dot);
+            float o = 0.f;
+#pragma unroll
+            for (int d = 0; d < DMAX; d++) { s[d] = fmaf(ks[tt][d], u, s[d]); o = fmaf(s[d], qs[tt][d], o); }
+            O[(size_t) t * H * V + (size_t) h * V + col] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int d = 0; d < DMAX; d++) if (d < D) Sh[(size_t) d * V + col] = s[d];
+    }
+}
+// Step 4: each head's read-out over its root mean square (eps inside the root), times the shared weight [V], times
+// silu(output gate). One warp per (token, head).
+__global__ void k_delta_out(const float * __restrict__ O, const float * __restrict__ P, int ldp, int gate_off, int H, int V,
+                            const float * __restrict__ normw, float eps, float * __restrict__ A) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int h = warp; h < H; h += nw) {
+        const float * o = O + (size_t) t * H * V + (size_t) h * V;
+        const float * gp = P + (size_t) t * ldp + gate_off + (size_t) h * V;
+        float ss = 0.f;
+        for (int i = lane; i < V; i += 32) ss = fmaf(o[i], o[i], ss);
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float) V + eps);
+        for (int i = lane; i < V; i += 32) A[(size_t) t * H * V + (size_t) h * V + i] = o[i] * r * normw[i] * siluf_(gp[i]);
+    }
+}
+
+// ---- clamped gated feed-forward: GU[t] = [ gate | up ] (biases included) --------------------------------------------------
+// g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha g) * (u + 1)
+__global__ void k_clamped_glu(const float * __restrict__ GU, int T, int ff, float limit, float alpha, float * __restrict__ ACT) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t) T * ff) return;
+    const size_t t = i / ff, c = i % ff;
+    const float g = fminf(GU[t * 2 * ff + c], limit);
+    const float u = fminf(fmaxf(GU[t * 2 * ff + ff + c], -limit), limit);
+    ACT[i] = g * sigmoidf_(alpha * g) * (u + 1.0f);
+}
+
+// ---- arg-max of one row of logits (lowest index wins ties) -----------------------------------------------------------------
+__global__ void __launch_bounds__(1024) k_argmax_row(const float * __restrict__ x, int n, int32_t * __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    float best = -INFINITY; int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = x[i]; if (v > best || (v == best && i < idx)) { best = v; idx = i; } }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int) (blockDim.x >> 5); w++) if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        *out = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
+}  // namespace stk
+}  // namespace b200

@@ -1,5 +1,6 @@
 // tokenizer.cpp — see tokenizer.hpp. Host-side only; every rule below cites the reference code it restates.
 #include "tokenizer.hpp"
+#include "safetensors.hpp"
 #include "gguf.hpp"
 #include "unicode_tables.hpp"
 
@@ -536,6 +537,16 @@ std::unique_ptr<Tokenizer> make_tokenizer(const std::string & gguf_path, std::st
     }
 }
 static std::unique_ptr<Tokenizer> make_tokenizer_impl(const std::string & gguf_path, std::string & err) {
+    std::string dir;
+    if (is_model_dir(gguf_path, &dir)) {
+        // folder models (config.json + model.safetensors) carry no vocabulary: prompts are decimal ids, like "no_vocab" GGUFs.
+        // "eos" in config.json, when given, ends a generation.
+        const Json cfg = json_parse_file(dir + "/config.json");
+        auto t = std::make_unique<IdTokenizer>();
+        t->nv = (int32_t) cfg.integer("vocab");
+        t->eos_id = (int32_t) cfg.integer("eos", -1);
+        return t;
+    }
     gguf_file g;
     err = g.open(gguf_path);
     if (!err.empty()) return nullptr;

@@ -25,9 +25,14 @@ def device_count() -> int:
 class Model:
     """llama_load_model_from_file (cpp/bridge.cpp:131) for one pipeline stage [layer_begin, layer_end)."""
 
-    def __init__(self, path: str, device: int = 0, layer_begin: int = 0, layer_end: int = -1):
+    def __init__(self, path: str, device: int = 0, layer_begin: int = 0, layer_end: int = -1, dtype: Optional[str] = None):
+        """path: a GGUF file (LLaMA path) or a folder with config.json + model.safetensors (layer-stack family, chosen
+        by the configuration's "architecture"); dtype ("bfloat16" | "float32") applies to folder models"""
         self.L = _lib.lib()
-        self.h = self.L.b200_model_load(path.encode(), device, layer_begin, layer_end)
+        if dtype is None:
+            self.h = self.L.b200_model_load(path.encode(), device, layer_begin, layer_end)
+        else:
+            self.h = self.L.b200_model_load_dtype(path.encode(), device, layer_begin, layer_end, dtype.encode())
         if not self.h:
             raise B200Error(f"b200_model_load({path}): {_lib.last_error()}")
         arr = (C.c_int32 * 16)()
@@ -94,6 +99,21 @@ class Context:
         check(self.L.b200_decode(self.h, toks.ctypes.data_as(C.POINTER(C.c_int32)), len(toks), pos0,
                                  out.ctypes.data_as(C.POINTER(C.c_float)) if want_logits else None), "b200_decode")
         return out
+
+    def decode_rows(self, tokens: Sequence[int], pos0: int, rows: Sequence[int]) -> np.ndarray:
+        """the step's tokens with the logits of the places `rows` (ascending indices into tokens): [len(rows), n_vocab]"""
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        rr = np.ascontiguousarray(rows, dtype=np.int32)
+        out = np.empty((len(rr), self.model.n_vocab), dtype=np.float32)
+        i32p = C.POINTER(C.c_int32)
+        check(self.L.b200_decode_rows(self.h, toks.ctypes.data_as(i32p), len(toks), pos0, rr.ctypes.data_as(i32p) if len(rr) else None,
+                                      len(rr), out.ctypes.data_as(C.POINTER(C.c_float)) if len(rr) else None), "b200_decode_rows")
+        return out
+
+    def layer_taps(self, n_tokens: int) -> np.ndarray:
+        """layer-stack models, after set_taps(True) and one step: the residual stream after every layer, [layers, tokens, width]"""
+        t = self.get_tap("l_out", -1)
+        return t.reshape(self.model.n_layer, n_tokens, self.model.n_embd)
 
     def generate_greedy(self, first_token: int, pos0: int, n_steps: int) -> np.ndarray:
         out = np.empty(n_steps, dtype=np.int32)

@@ -46,6 +46,14 @@ const char * b200_version(void);
  * b200_ctx_new        replaces llama_new_context_with_model (cpp/bridge.cpp:162; cpp/src/llama.cpp:16592-16993):
  *                     f16 KV cache for the stage's layers (:2926-3022), n_ctx padded to 32 (:16655).            */
 b200_model * b200_model_load(const char * gguf_path, int device, int layer_begin, int layer_end);
+/* Model registry by container. A path that is a folder holding config.json + model.safetensors (or that config.json itself)
+ * is a model of the layer-stack family: config.json names the design in "architecture" (registered: "Matulorn") and lists
+ * the layers, each one mixer ("mingru", "latent_attention", "delta") and an optional feed-forward. dtype = "bfloat16"
+ * (default when NULL: matrices stay bfloat16, 32-bit accumulation; norms, recurrences, attention weights and the residual
+ * stream in float32) or "float32" (everything in true 32-bit on the CUDA cores). b200_model_load on such a path uses the
+ * environment's BOOSTER_B200_DTYPE or bfloat16. The family keeps all layers on one device; tokens are decimal ids
+ * ("no_vocab"). A GGUF path behaves like b200_model_load. */
+b200_model * b200_model_load_dtype(const char * path, int device, int layer_begin, int layer_end, const char * dtype);
 void         b200_model_free(b200_model * m);
 
 enum { B200_INFO_N_VOCAB = 0, B200_INFO_N_EMBD, B200_INFO_N_LAYER, B200_INFO_N_HEAD, B200_INFO_N_HEAD_KV,
@@ -86,6 +94,11 @@ int b200_kv_seq_div(b200_ctx * c, int p0, int p1, int d);
  *                (the only row llama_batch_get_one keeps). logits_out may be NULL (prompt chunks).
  *                Single-stage contexts only; pipeline stages use b200_stage_step.                            */
 int b200_decode(b200_ctx * c, const int32_t * tokens, int n, int pos0, float * logits_out);
+/* b200_decode with the logits of chosen places of the step: rows[n_rows] ascending indices into tokens, logits_out
+ * [n_rows][n_vocab] (n_rows may be 0). Layer-stack models run the head on exactly those rows; GGUF models keep the last
+ * row of a step only and accept rows = {n - 1}. Layer-stack contexts hold ONE sequence with recurrent state: pos0 must
+ * continue it (b200_kv_clear starts a new sequence), and a step may cut the token stream anywhere. */
+int b200_decode_rows(b200_ctx * c, const int32_t * tokens, int n, int pos0, const int32_t * rows, int n_rows, float * logits_out);
 
 /* Device-resident greedy loop: token → decode → argmax → next token, n_steps times, one CUDA-graph replay
  * per token, no host round trip between tokens. Equivalent to the reference loop cpp/bridge.cpp:467-646 with
@@ -106,6 +119,10 @@ int64_t b200_get_tap(b200_ctx * c, const char * name, int layer, float * out, in
 /* µs-resolution counters (the reference's are ms-truncated at the bridge: cpp/bridge.cpp:650-655) */
 void b200_timings(b200_ctx * c, double * t_prompt_us, int64_t * n_prompt, double * t_gen_us, int64_t * n_gen);
 void b200_reset_timings(b200_ctx * c);
+/* mean ms of one [T x K] . [N x K]^T product through the layer-stack family's own kernels (dtype 0 bfloat16, 1 float32;
+ * T <= 4 takes the decode mat-vec, larger T the prompt kernels), CUDA events around `reps` launches over distinct weights;
+ * negative on error. bench.py's per-kernel roofline of the family. */
+float b200_stack_time_linear(int device, int dtype, int T, int N, int K, int reps);
 /* number of kernels launched by this library's own code since the context was created */
 int64_t b200_kernel_launches(const b200_ctx * c);
 /* device time (CUDA events on the engine's stream) of the last b200_generate_greedy /
