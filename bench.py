@@ -218,6 +218,107 @@ def bridge_e2e(path, ctx, n_prompt, n_gen, reps):
     return best
 
 
+# ---- layer-stack family (Matulorn design) beside the LLaMA path at equal layer sizes: `--family stack` ------------------------
+STACK_SIZES = {
+    # width, layers, ff, heads: layers that resemble a 1B-class and an 8B-class model (fewer of them: the weights are random)
+    "w2048": dict(width=2048, n_layer=8, ff=8192, heads=16),
+    "w4096": dict(width=4096, n_layer=4, ff=14336, heads=32),
+}
+
+
+def bench_stack(args):
+    """Prefill and decode throughput of the Matulorn design (bfloat16 weights; random) at sizes resembling real layers, the
+    LLaMA path (Q8_0, the closest block format in bytes per weight) at equal width / ff / layers / vocabulary beside it, and
+    the per-kernel roofline fractions of both: the mat-vec of decode against the measured HBM copy bandwidth, the prompt
+    product against the measured cuBLAS bf16 rate. One JSON line; the default workload of this file is untouched."""
+    from booster_b200 import _lib, engine, stack_io
+    L = _lib.lib()
+    hbm, hbm_src = peaks()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tflops = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        tflops = 1590.0
+    out = {"family": "stack", "design": "Matulorn", "dtype": "bf16", "data": "synthetic (random bfloat16 weights)", "hbm_gbs_peak": hbm,
+           "hbm_peak_source": hbm_src, "bf16_tflops_peak": tflops, "steps": args.steps, "warmup": args.warmup, "sizes": {}}
+    n_prompt, n_gen = 2048, 64
+    for name, sz in STACK_SIZES.items():
+        if args.stack_size and name != args.stack_size:
+            continue
+        res = {}
+        cfg = stack_io.matulorn_config(**sz)
+        d = os.path.join(MODEL_DIR, f"matulorn_{name}_s1234")
+        if not os.path.exists(os.path.join(d, "config.json")):
+            stack_io.synth_stack(d, cfg)
+        m = engine.Model(d, dtype="bfloat16")
+        c = engine.Context(m, n_prompt + n_gen * (args.steps + args.warmup) + 8)
+        prompt = np.random.default_rng(42).integers(0, cfg["vocab"], size=n_prompt).tolist()
+        pre = []
+        for i in range(args.warmup + args.steps):
+            c.kv_clear()
+            c.decode(prompt, 0)
+            if i >= args.warmup:
+                pre.append(c.last_device_ms())
+        pos, tok, dec = n_prompt, 1, []
+        for i in range(args.warmup + args.steps):
+            ids = c.generate_greedy(tok, pos, n_gen)
+            pos += n_gen; tok = int(ids[-1])
+            if i >= args.warmup:
+                dec.append(c.last_device_ms())
+        res["matulorn"] = {"params": stack_io.n_params(cfg), "weight_bytes_per_token": m.weight_bytes, "layers": [l["type"] for l in cfg["layers"]],
+                           "prefill_tok_s": n_prompt / (np.median(pre) / 1e3), "prefill_tokens": n_prompt,
+                           "decode_tok_s": n_gen / (np.median(dec) / 1e3), "decode_n_kv": [n_prompt, pos],
+                           "decode_hbm_frac": m.weight_bytes * n_gen / (np.median(dec) / 1e3) / (hbm * 1e9),
+                           "kernel_launches": int(L.b200_kernel_launches(c.h))}
+        c.close(); m.close()
+        # the family's products alone: decode mat-vec (T = 1) and prompt product (T = 512) of the gate|up and down shapes
+        E, ff = sz["width"], sz["ff"]
+        kern = {}
+        for label, (N, K) in {"gate_up": (2 * ff, E), "down": (E, ff)}.items():
+            ms1 = L.b200_stack_time_linear(0, 0, 1, N, K, 50)
+            ms512 = L.b200_stack_time_linear(0, 0, 512, N, K, 20)
+            kern[label] = {"matvec_us": 1e3 * ms1, "matvec_hbm_frac": N * K * 2 / (ms1 / 1e3) / (hbm * 1e9),
+                           "prompt512_us": 1e3 * ms512, "prompt512_tflops": 2.0 * 512 * N * K / (ms512 / 1e3) / 1e12,
+                           "prompt512_frac_of_bf16_peak": 2.0 * 512 * N * K / (ms512 / 1e3) / 1e12 / tflops}
+        res["matulorn"]["kernels"] = kern
+        # the closest existing model at equal size: LLaMA layers (attention + SwiGLU) in Q8_0 blocks
+        lc = G.LlamaConfig(n_layer=sz["n_layer"], n_embd=E, n_head=sz["heads"], n_head_kv=max(1, sz["heads"] // 4), n_ff=ff, n_vocab=32000,
+                           n_ctx_train=8192, name=f"synthetic-llama-{name}")
+        lp = os.path.join(MODEL_DIR, f"llama_{name}_Q8_0_s1234.gguf")
+        if not os.path.exists(lp):
+            G.synth_llama(lp + ".tmp", lc, "Q8_0", seed=1234, source="blocks")
+            os.replace(lp + ".tmp", lp)
+        lm = engine.Model(lp)
+        lctx = engine.Context(lm, n_prompt + n_gen * (args.steps + args.warmup) + 8)
+        lprompt = np.random.default_rng(42).integers(0, 32000, size=n_prompt).tolist()
+        pre = []
+        for i in range(args.warmup + args.steps):
+            lctx.kv_clear()
+            t0 = time.perf_counter()
+            for j in range(0, n_prompt, 512):
+                lctx.decode(lprompt[j:j + 512], j, want_logits=(j + 512 >= n_prompt))
+            if i >= args.warmup:
+                pre.append(1e3 * (time.perf_counter() - t0))
+        pos, tok, dec = n_prompt, 1, []
+        for i in range(args.warmup + args.steps):
+            ids = lctx.generate_greedy(tok, pos, n_gen)
+            pos += n_gen; tok = int(ids[-1])
+            if i >= args.warmup:
+                dec.append(lctx.last_device_ms())
+        prof = lctx.profile_token(1, pos)
+        gu_ms, gu_n = prof["gate_up"]
+        gu_bytes = 2 * ff * E * 34 / 32
+        res["llama_q8_0"] = {"weight_bytes_per_token": lm.weight_bytes, "prefill_tok_s": n_prompt / (np.median(pre) / 1e3),
+                             "prefill_timing": "wall clock around four 512-token batches", "decode_tok_s": n_gen / (np.median(dec) / 1e3),
+                             "decode_hbm_frac": lm.weight_bytes * n_gen / (np.median(dec) / 1e3) / (hbm * 1e9),
+                             "kernels": {"gate_up": {"matvec_us": 1e3 * gu_ms / max(gu_n, 1),
+                                                     "matvec_hbm_frac": gu_bytes / (gu_ms / max(gu_n, 1) / 1e3) / (hbm * 1e9)}}}
+        lctx.close(); lm.close()
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -227,7 +328,12 @@ def main():
     ap.add_argument("--config", default=DEFAULT_CONFIG, choices=sorted(BENCH_CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg (A/B runs of the GPU path only)")
     ap.add_argument("--value-only", action="store_true", help="A/B runs: device-resident value only (no e2e / roofline / cpu legs)")
+    ap.add_argument("--family", default="llama", choices=["llama", "stack"],
+                    help="stack: the layer-stack family (Matulorn design) beside the LLaMA path at equal layer sizes; the default workload is untouched")
+    ap.add_argument("--stack-size", default="", choices=[""] + sorted(STACK_SIZES), help="--family stack: one size only")
     args = ap.parse_args()
+    if args.family == "stack":
+        return bench_stack(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -301,12 +301,19 @@ void build_matulorn(StackModel & m, const Json & cfg, const safetensors_file & s
             L.limit = (float) mj.number("limit");
             L.norm2 = up_f32(m, sf.read_f32(p + "norm2", {E}));
             L.norm2b = up_f32(m, sf.read_f32(p + "norm2b", {E}));
-            std::vector<float> W = sf.read_f32(p + "mlp.gate", {ff, E}), b = sf.read_f32(p + "mlp.gate.b", {ff});
-            append(W, sf.read_f32(p + "mlp.up", {ff, E})); append(b, sf.read_f32(p + "mlp.up.b", {ff}));
+            // gate and up interleaved row by row (2i: gate_i, 2i + 1: up_i): the product's epilogue holds both halves of a unit
+            const std::vector<float> Wg = sf.read_f32(p + "mlp.gate", {ff, E}), bg = sf.read_f32(p + "mlp.gate.b", {ff});
+            const std::vector<float> Wu = sf.read_f32(p + "mlp.up", {ff, E}), bu = sf.read_f32(p + "mlp.up.b", {ff});
+            std::vector<float> W((size_t) 2 * ff * E), b((size_t) 2 * ff);
+            for (int i = 0; i < ff; i++) {
+                std::memcpy(&W[(size_t) (2 * i) * E], &Wg[(size_t) i * E], (size_t) E * 4);
+                std::memcpy(&W[(size_t) (2 * i + 1) * E], &Wu[(size_t) i * E], (size_t) E * 4);
+                b[(size_t) 2 * i] = bg[(size_t) i]; b[(size_t) 2 * i + 1] = bu[(size_t) i];
+            }
             L.gateup = up_mat(m, W, 2 * ff, E, &b);
             const std::vector<float> db = sf.read_f32(p + "mlp.down.b", {E});
             L.down = up_mat(m, sf.read_f32(p + "mlp.down", {E, ff}), E, ff, &db);
-            m.maxP = std::max(m.maxP, 2 * ff); m.maxA = std::max(m.maxA, ff);
+            m.maxA = std::max(m.maxA, ff);
         }
         m.weight_bytes += (int64_t) E * 4 * (L.has_mlp ? 4 : 2);
     }
@@ -326,16 +333,21 @@ bool mma_enabled() {
 }
 
 void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, int ldx, const void * W, const float * bias, float * Y, int ldy,
-               int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0) {
+               int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f) {
     if (T <= 0 || N <= 0) return;
-    LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0};
+    LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0, glu ? 1 : 0, glu_limit, GLU_ALPHA};
     const int vecw = dtype == STACK_F32 ? 4 : 8;
     const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
     a.vec = K % vecw == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % vecw == 0 && al16(X) && al16(W);
     if (launches) (*launches)++;
     if (T <= GEMV_MAX_T) {
-        const dim3 grid((unsigned) ((N + 7) / 8), 1, (unsigned) batch);
-        if (dtype == STACK_F32) k_gemv<float><<<grid, 256, 0, st>>>(a); else k_gemv<__nv_bfloat16><<<grid, 256, 0, st>>>(a);
+        if (a.glu) {
+            const dim3 grid((unsigned) ((N / 2 + 7) / 8), 1, (unsigned) batch);
+            if (dtype == STACK_F32) k_gemv<float, 2><<<grid, 256, 0, st>>>(a); else k_gemv<__nv_bfloat16, 2><<<grid, 256, 0, st>>>(a);
+        } else {
+            const dim3 grid((unsigned) ((N + 7) / 8), 1, (unsigned) batch);
+            if (dtype == STACK_F32) k_gemv<float, 1><<<grid, 256, 0, st>>>(a); else k_gemv<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(a);
+        }
     } else if (dtype == STACK_BF16 && a.vec && mma_enabled()) {
         const dim3 grid((unsigned) ((N + MM_BN - 1) / MM_BN), (unsigned) ((T + MM_BM - 1) / MM_BM), (unsigned) batch);
         k_gemm_bf16_mma<<<grid, 256, 0, st>>>(a);
@@ -346,8 +358,15 @@ void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, 
     SCU(cudaGetLastError());
 }
 
-void linear(StackCtx * c, const float * X, int ldx, const DMat & W, float * Y, int ldy, int T, int batch = 1, long long sX = 0, long long sY = 0) {
-    linear_on(c->st, c->m->dtype, &c->launches, X, ldx, W.w, W.bias, Y, ldy, T, W.N, W.K, batch, sX, (long long) W.N * W.K, sY);
+void linear(StackCtx * c, const float * X, int ldx, const DMat & W, float * Y, int ldy, int T, int batch = 1, long long sX = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f) {
+    linear_on(c->st, c->m->dtype, &c->launches, X, ldx, W.w, W.bias, Y, ldy, T, W.N, W.K, batch, sX, (long long) W.N * W.K, sY, glu, glu_limit);
+}
+
+// end of a sub-layer: X += norm(Y) * w_post; Hn = norm(X) * w_next when another sub-layer follows
+void post_norm_add(StackCtx * c, const float * w_post, const float * w_next, int T) {
+    const StackModel & m = *c->m;
+    k_post_norm_add<<<T, std::min(256, 32 * m.groups), 0, c->st>>>(c->Y, w_post, c->X, w_next, c->Hn, m.E, m.groups, m.eps);
+    c->launches++;
 }
 
 void norm(StackCtx * c, const float * X, int ldx, const int32_t * rows, const float * w, int n, int groups, float * Y, int ldy, int T, bool accumulate) {
@@ -413,26 +432,24 @@ void tap_layer(StackCtx * c, size_t li, int T) {
 void enqueue_layers(StackCtx * c, int T) {
     StackModel & m = *c->m;
     const int E = m.E;
-    if (m.dtype == STACK_F32) k_embed_rows<float><<<T, 128, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, c->X);
-    else k_embed_rows<__nv_bfloat16><<<T, 128, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, c->X);
+    const int nthreads = std::min(256, std::max(128, 32 * m.groups));
+    const float * w0 = m.layers[0].norm1;
+    if (m.dtype == STACK_F32) k_embed_rows<float><<<T, nthreads, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, c->X, w0, m.groups, m.eps, c->Hn);
+    else k_embed_rows<__nv_bfloat16><<<T, nthreads, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, c->X, w0, m.groups, m.eps, c->Hn);
     c->launches++;
     for (size_t li = 0; li < m.layers.size(); li++) {
         const LayerSpec & L = m.layers[li];
-        norm(c, c->X, E, nullptr, L.norm1, E, m.groups, c->Hn, E, T, false);
-        switch (L.kind) {
+        const float * next_in = li + 1 < m.layers.size() ? m.layers[li + 1].norm1 : nullptr;     // the final norm runs on the wanted rows only
+        switch (L.kind) {                              // Hn holds norm1(x)
             case MIX_MINGRU: mixer_mingru(c, L, T); break;
             case MIX_LATENT: mixer_latent(c, L, T); break;
             default:         mixer_delta(c, L, T); break;
         }
-        norm(c, c->Y, E, nullptr, L.norm1b, E, m.groups, c->X, E, T, true);
+        post_norm_add(c, L.norm1b, L.has_mlp ? L.norm2 : next_in, T);
         if (L.has_mlp) {
-            norm(c, c->X, E, nullptr, L.norm2, E, m.groups, c->Hn, E, T, false);
-            linear(c, c->Hn, E, L.gateup, c->P, 2 * L.ff, T);
-            const size_t n = (size_t) T * L.ff;
-            k_clamped_glu<<<(unsigned) ((n + 255) / 256), 256, 0, c->st>>>(c->P, T, L.ff, L.limit, GLU_ALPHA, c->A);
-            c->launches++;
+            linear(c, c->Hn, E, L.gateup, c->A, L.ff, T, 1, 0, 0, true, L.limit);      // clamped gated unit in the epilogue
             linear(c, c->A, L.ff, L.down, c->Y, E, T);
-            norm(c, c->Y, E, nullptr, L.norm2b, E, m.groups, c->X, E, T, true);
+            post_norm_add(c, L.norm2b, next_in, T);
         }
         if (c->taps) tap_layer(c, li, T);
     }

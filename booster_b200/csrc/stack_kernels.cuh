@@ -37,13 +37,49 @@ struct StepState {
     int32_t n_tokens;
 };
 
-// ---- embedding: X[t] = embed[token[t]] ----------------------------------------------------------------------
+// ---- RMS norm of one group by one warp: y = x / sqrt(mean(x^2) + eps) * w ------------------------------------------------
+__device__ __forceinline__ void warp_group_norm(const float * __restrict__ x, const float * __restrict__ w, int gs, float eps, float * __restrict__ y, int lane) {
+    float ss = 0.f;
+    for (int i = lane; i < gs; i += 32) { const float v = x[i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float) gs + eps);
+    for (int i = lane; i < gs; i += 32) y[i] = x[i] * r * w[i];
+}
+
+// ---- embedding fused with the first layer's input norm: X[t] = embed[token[t]], Hn[t] = norm(X[t]) * w ---------------------
 template <typename WT>
-__global__ void k_embed_rows(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, float * __restrict__ X) {
+__global__ void k_embed_rows(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, float * __restrict__ X,
+                             const float * __restrict__ w, int groups, float eps, float * __restrict__ Hn) {
     const int t = blockIdx.x;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : tok >= n_vocab ? n_vocab - 1 : tok;      // ids are validated on the host; never read outside the table
     for (int i = threadIdx.x; i < E; i += blockDim.x) X[(size_t) t * E + i] = wf(embed, (size_t) tok * E + i);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, gs = E / groups;
+    for (int g = warp; g < groups; g += nw) warp_group_norm(X + (size_t) t * E + g * gs, w + g * gs, gs, eps, Hn + (size_t) t * E + g * gs, lane);
+}
+
+// ---- end of a sub-layer, fused: X[t] += norm(Y[t]) * w_post, then (w_next != nullptr) Hn[t] = norm(X[t]) * w_next, the input
+// norm of the sub-layer that follows. Same groups for both; one block per row, one warp per group.
+__global__ void k_post_norm_add(const float * __restrict__ Y, const float * __restrict__ w_post, float * __restrict__ X,
+                                const float * __restrict__ w_next, float * __restrict__ Hn, int n, int groups, float eps) {
+    const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, gs = n / groups;
+    for (int g = warp; g < groups; g += nw) {
+        const size_t b = (size_t) row * n + (size_t) g * gs;
+        const float * y = Y + b;
+        float * x = X + b;
+        float ss = 0.f;
+        for (int i = lane; i < gs; i += 32) ss = fmaf(y[i], y[i], ss);
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float) gs + eps);
+        float s2 = 0.f;
+        for (int i = lane; i < gs; i += 32) { const float v = x[i] + y[i] * r * w_post[g * gs + i]; x[i] = v; s2 = fmaf(v, v, s2); }
+        if (w_next) {
+            s2 = warp_sum(s2);
+            const float r2 = 1.0f / sqrtf(s2 / (float) gs + eps);
+            for (int i = lane; i < gs; i += 32) Hn[b + i] = x[i] * r2 * w_next[g * gs + i];     // each lane re-reads what it wrote
+        }
+    }
 }
 
 // ---- RMS norm in `groups` equal consecutive parts; eps inside the root ----------------------------------------------
@@ -76,32 +112,43 @@ struct LinArgs {
     int T, N, K, ldx, ldy;
     long long sX, sW, sY;
     int vec;            // 1: K, ldx and all bases allow 16-byte loads
+    int glu;            // 1: rows of W are interleaved (2i: gate_i, 2i + 1: up_i); the epilogue writes the clamped gated unit
+    float limit, alpha; //    y_i = g sigmoid(alpha g) (u + 1), g = min(gate_i, limit), u = clamp(up_i, -limit, limit), to Y[t][i] (N / 2 wide)
 };
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g * sigmoidf_(alpha * g) * (u + 1.0f);
+}
 
 constexpr int GEMV_MAX_T = 4;
 // decode and very short portions: one warp per output row, the row of W streamed once with 16-byte loads
-template <typename WT>
+template <typename WT, int RPW>
 __global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+    const int n = (blockIdx.x * (blockDim.x >> 5) + warp) * RPW;      // RPW = 2: a (gate, up) pair per warp
     if (n >= a.N) return;
     const WT * w = reinterpret_cast<const WT *>(a.W) + (size_t) blockIdx.z * a.sW + (size_t) n * a.K;
     const float * x = a.X + (size_t) blockIdx.z * a.sX;
-    float acc[GEMV_MAX_T];
+    float acc[RPW][GEMV_MAX_T];
 #pragma unroll
-    for (int t = 0; t < GEMV_MAX_T; t++) acc[t] = 0.f;
+    for (int r = 0; r < RPW; r++)
+#pragma unroll
+        for (int t = 0; t < GEMV_MAX_T; t++) acc[r][t] = 0.f;
     constexpr int VEC = 16 / (int) sizeof(WT);
     if (a.vec) {
         for (int k = lane * VEC; k < a.K; k += 32 * VEC) {
-            float wv[VEC];
-            if constexpr (sizeof(WT) == 2) {
-                const uint4 u = *reinterpret_cast<const uint4 *>(w + k);
-                const uint32_t uu[4] = { u.x, u.y, u.z, u.w };
+            float wv[RPW][VEC];
 #pragma unroll
-                for (int i = 0; i < 4; i++) { wv[2 * i] = __uint_as_float(uu[i] << 16); wv[2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u); }
-            } else {
-                const float4 f = *reinterpret_cast<const float4 *>(w + k);
-                wv[0] = f.x; wv[1] = f.y; wv[2] = f.z; wv[3] = f.w;
+            for (int r = 0; r < RPW; r++) {
+                if constexpr (sizeof(WT) == 2) {
+                    const uint4 u = *reinterpret_cast<const uint4 *>(w + (size_t) r * a.K + k);
+                    const uint32_t uu[4] = { u.x, u.y, u.z, u.w };
+#pragma unroll
+                    for (int i = 0; i < 4; i++) { wv[r][2 * i] = __uint_as_float(uu[i] << 16); wv[r][2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u); }
+                } else {
+                    const float4 f = *reinterpret_cast<const float4 *>(w + (size_t) r * a.K + k);
+                    wv[r][0] = f.x; wv[r][1] = f.y; wv[r][2] = f.z; wv[r][3] = f.w;
+                }
             }
 #pragma unroll
             for (int t = 0; t < GEMV_MAX_T; t++) {
@@ -110,24 +157,36 @@ __global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
 #pragma unroll
                     for (int i = 0; i < VEC; i += 4) {
                         const float4 xv = *reinterpret_cast<const float4 *>(xt + i);
-                        acc[t] = fmaf(wv[i], xv.x, acc[t]); acc[t] = fmaf(wv[i + 1], xv.y, acc[t]);
-                        acc[t] = fmaf(wv[i + 2], xv.z, acc[t]); acc[t] = fmaf(wv[i + 3], xv.w, acc[t]);
+#pragma unroll
+                        for (int r = 0; r < RPW; r++) {
+                            acc[r][t] = fmaf(wv[r][i], xv.x, acc[r][t]); acc[r][t] = fmaf(wv[r][i + 1], xv.y, acc[r][t]);
+                            acc[r][t] = fmaf(wv[r][i + 2], xv.z, acc[r][t]); acc[r][t] = fmaf(wv[r][i + 3], xv.w, acc[r][t]);
+                        }
                     }
                 }
             }
         }
     } else {
         for (int k = lane; k < a.K; k += 32) {
-            const float wv = wf(w, k);
 #pragma unroll
-            for (int t = 0; t < GEMV_MAX_T; t++) if (t < a.T) acc[t] = fmaf(wv, x[(size_t) t * a.ldx + k], acc[t]);
+            for (int r = 0; r < RPW; r++) {
+                const float wv = wf(w, (size_t) r * a.K + k);
+#pragma unroll
+                for (int t = 0; t < GEMV_MAX_T; t++) if (t < a.T) acc[r][t] = fmaf(wv, x[(size_t) t * a.ldx + k], acc[r][t]);
+            }
         }
     }
 #pragma unroll
     for (int t = 0; t < GEMV_MAX_T; t++) {
         if (t < a.T) {
-            const float s = warp_sum(acc[t]);
-            if (lane == 0) a.Y[(size_t) blockIdx.z * a.sY + (size_t) t * a.ldy + n] = s + (a.bias ? a.bias[n] : 0.f);
+            float s[RPW];
+#pragma unroll
+            for (int r = 0; r < RPW; r++) s[r] = warp_sum(acc[r][t]) + (a.bias ? a.bias[n + r] : 0.f);
+            if (lane == 0) {
+                float * y = a.Y + (size_t) blockIdx.z * a.sY + (size_t) t * a.ldy;
+                if constexpr (RPW == 2) y[n >> 1] = clamped_glu(s[0], s[1], a.limit, a.alpha);
+                else y[n] = s[0];
+            }
         }
     }
 }
@@ -188,6 +247,14 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
     for (int i = 0; i < 4; i++) {
         const int m = m0 + ty * 4 + i;
         if (m >= a.T) continue;
+        if (a.glu) {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < a.N) Y[(size_t) m * a.ldy + (n >> 1)] = clamped_glu(acc[i][j] + (a.bias ? a.bias[n] : 0.f), acc[i][j + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha);
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
@@ -285,7 +352,10 @@ __global__ void __launch_bounds__(256) k_gemm_bf16_mma(const LinArgs a) {
             for (int e = 0; e < 4; e++) {
                 const int m = m0 + wm + 16 * i + (lane >> 2) + (e >> 1) * 8;
                 const int n = n0 + wn + 8 * j + (lane & 3) * 2 + (e & 1);
-                if (m < a.T && n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j][e] + (a.bias ? a.bias[n] : 0.f);
+                if (a.glu) {            // this thread holds the (gate, up) pair of unit n / 2 in elements e, e + 1
+                    if (!(e & 1) && m < a.T && n + 1 < a.N)
+                        Y[(size_t) m * a.ldy + (n >> 1)] = clamped_glu(acc[i][j][e] + (a.bias ? a.bias[n] : 0.f), acc[i][j][e + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha);
+                } else if (m < a.T && n < a.N) Y[(size_t) m * a.ldy + n] = acc[i][j][e] + (a.bias ? a.bias[n] : 0.f);
             }
 }
 
@@ -519,17 +589,6 @@ __global__ void k_delta_out(const float * __restrict__ O, const float * __restri
         const float r = 1.0f / sqrtf(ss / (float) V + eps);
         for (int i = lane; i < V; i += 32) A[(size_t) t * H * V + (size_t) h * V + i] = o[i] * r * normw[i] * siluf_(gp[i]);
     }
-}
-
-// ---- clamped gated feed-forward: GU[t] = [ gate | up ] (biases included) --------------------------------------------------
-// g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha g) * (u + 1)
-__global__ void k_clamped_glu(const float * __restrict__ GU, int T, int ff, float limit, float alpha, float * __restrict__ ACT) {
-    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t) T * ff) return;
-    const size_t t = i / ff, c = i % ff;
-    const float g = fminf(GU[t * 2 * ff + c], limit);
-    const float u = fminf(fmaxf(GU[t * 2 * ff + ff + c], -limit), limit);
-    ACT[i] = g * sigmoidf_(alpha * g) * (u + 1.0f);
 }
 
 // ---- arg-max of one row of logits (lowest index wins ties) -----------------------------------------------------------------
