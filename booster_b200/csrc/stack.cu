@@ -105,7 +105,12 @@ struct StackCtx {
     cudaGraphExec_t g_token = nullptr;    // one token: header in -> layers -> head -> logits out
     bool graph_failed = false;
     int64_t n_token_launches = 0;         // kernels per replay of g_token
-    size_t attn_smem = 0;
+    size_t attn_smem = 0;                 // the most dynamic shared memory any attention launch of this context asks for
+    float * att_scores = nullptr;         // prompt attention: scores / weights of a group of tiles
+    size_t att_scores_floats = 0;
+    std::vector<float *> cache_allocs;    // the caches with their zero margins (caches[] point behind the front margin)
+    float * att_part = nullptr, * att_ml = nullptr;   // key-slice partials of the latent attention (decode)
+    int sm_count = 148;
     bool taps = false;
     std::vector<float> tap_data;
     int tap_T = 0;
@@ -335,7 +340,7 @@ bool mma_enabled() {
 void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, int ldx, const void * W, const float * bias, float * Y, int ldy,
                int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f) {
     if (T <= 0 || N <= 0) return;
-    LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0, glu ? 1 : 0, glu_limit, GLU_ALPHA};
+    LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0, glu ? 1 : 0, glu_limit, GLU_ALPHA, 0, 0};
     const int vecw = dtype == STACK_F32 ? 4 : 8;
     const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
     a.vec = K % vecw == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % vecw == 0 && al16(X) && al16(W);
@@ -391,6 +396,40 @@ void mixer_mingru(StackCtx * c, const LayerSpec & L, int T) {
     linear(c, c->A, L.width, L.o, c->Y, c->m->E, T);
 }
 
+// launch shape of the latent attention for a pass of T tokens: queries per block, key slices, shared memory
+struct AttnPlan { int TQ, HQ, nsplit, smax; size_t smem; };
+AttnPlan plan_attention(const LayerSpec & L, int n_ctx, int T, int sm_count) {
+    AttnPlan p;
+    p.TQ = std::min(T, 4);
+    p.HQ = std::min(L.H, std::max(1, LAT_NQ_MAX / p.TQ));
+    if (T < 8) p.HQ = std::min(p.HQ, 4);
+    const int W = L.rank + L.R;
+    const int keys = L.window > 0 ? std::min(L.window + p.TQ - 1, n_ctx) : n_ctx;     // the most keys a tile can see
+    const int blocks = ((T + p.TQ - 1) / p.TQ) * ((L.H + p.HQ - 1) / p.HQ);
+    p.nsplit = 1;
+    if (blocks < sm_count) p.nsplit = std::max(1, std::min({ 2 * sm_count / blocks, (keys + 31) / 32, 64 }));
+    for (;;) {
+        p.smax = (keys + p.nsplit - 1) / p.nsplit;
+        p.smem = ((size_t) p.TQ * p.HQ * (W + p.smax + 1) + 8) * 4;
+        if (p.smem <= 200 * 1024 || p.nsplit >= 64) break;
+        p.nsplit *= 2;                    // long unmasked contexts: slice the keys until the scores of a block fit
+    }
+    while (p.smem > 200 * 1024 && p.HQ > 1) { p.HQ = (p.HQ + 1) / 2; p.smem = ((size_t) p.TQ * p.HQ * (W + p.smax + 1) + 8) * 4; }
+    return p;
+}
+
+// float32 product on the CUDA cores with explicit operand layout (the attention's two products over cached rows)
+void gemm_f32(StackCtx * c, const float * X, int ldx, long long sX, const float * W, int w_kn, int ldw, long long sW, float * Y, int ldy, long long sY,
+              int M, int N, int K, int batch) {
+    const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
+    LinArgs a{X, W, nullptr, Y, M, N, K, ldx, ldy, sX, sW, sY, 0, 0, 0.f, 0.f, w_kn, ldw};
+    a.vec = K % 4 == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % 4 == 0 && al16(X) && al16(W);
+    k_gemm_simt<float><<<dim3((unsigned) ((N + 63) / 64), (unsigned) ((M + 63) / 64), (unsigned) batch), 256, 0, c->st>>>(a);
+    c->launches++;
+}
+constexpr int ATT_TQ = 16;                 // tokens per tile of the prompt attention
+constexpr size_t ATT_SCORE_BYTES = (size_t) 256 << 20;
+
 void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
     const int E = c->m->E, H = L.H, D = L.D, R = L.R, rank = L.rank, V = L.V, W = rank + R;
     const int ldp = H * (D + R) + W;
@@ -400,7 +439,32 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
     k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK);
     // absorbed queries, one product per head: QK[t][h][0..rank) = W_uk,h^T q[t][h][0..D)
     linear(c, c->P, ldp, L.ukT, c->QK, H * W, T, H, D + R, W);
-    k_latent_attn<<<dim3((unsigned) T, (unsigned) H), 256, c->attn_smem, c->st>>>(c->QK, cache, H, rank, R, L.window, L.scale, L.sink, &c->d_step->st, c->OL);
+    if (T >= 8) {
+        // prompt portion: scores, row soft-max and weighted sum as float32 products over tiles of ATT_TQ tokens x all heads
+        const int TQ = ATT_TQ, M = TQ * H, ntile = (T + TQ - 1) / TQ;
+        const int pos0 = c->h_step->st.pos0;                                       // of this pass (set by the step function before the launches)
+        const int nk = ((L.window > 0 ? L.window + TQ - 1 : pos0 + ntile * TQ) + 3) / 4 * 4;   // keys a tile's rows can see (unmasked: all so far), padded for 16-byte rows
+        const int per_group = (int) std::max<size_t>(1, c->att_scores_floats / ((size_t) M * nk));
+        for (int g0 = 0; g0 < ntile; g0 += per_group) {
+            const int ng = std::min(per_group, ntile - g0);
+            const long long jlo = L.window > 0 ? (long long) pos0 + (long long) g0 * TQ - L.window + 1 : 0;     // may be negative: the cache has a zero margin in front
+            const float * keys = cache + jlo * W;
+            const long long sK = L.window > 0 ? (long long) TQ * W : 0;
+            gemm_f32(c, c->QK + (size_t) g0 * M * W, W, (long long) M * W, keys, 0, 0, sK, c->att_scores, nk, (long long) M * nk, M, nk, W, ng);
+            const int rows = (std::min(T, (g0 + ng) * TQ) - g0 * TQ) * H;
+            k_latent_softmax_rows<<<(rows + 7) / 8, 256, 0, c->st>>>(c->att_scores, rows, H, TQ, nk, L.window, L.sink, &c->d_step->st, L.scale, g0);
+            gemm_f32(c, c->att_scores, nk, (long long) M * nk, keys, 1, W, sK, c->OL + (size_t) g0 * M * rank, rank, (long long) M * rank, M, rank, nk, ng);
+            c->launches++;
+        }
+        linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
+        linear(c, c->A, H * V, L.o, c->Y, E, T);
+        c->launches++;
+        return;
+    }
+    const AttnPlan ap = plan_attention(L, c->n_ctx, T, c->sm_count);
+    const LatAttnArgs aa{c->QK, cache, L.sink, &c->d_step->st, c->OL, c->att_part, c->att_ml, T, H, rank, R, L.window, L.scale, ap.TQ, ap.HQ, ap.nsplit, ap.smax};
+    k_latent_attn<<<dim3((unsigned) ((T + ap.TQ - 1) / ap.TQ), (unsigned) ((H + ap.HQ - 1) / ap.HQ), (unsigned) ap.nsplit), 256, ap.smem, c->st>>>(aa);
+    if (ap.nsplit > 1) { k_latent_combine<<<dim3((unsigned) T, (unsigned) H), 128, 0, c->st>>>(aa); c->launches++; }
     // values, one product per head: A[t][h] = W_uv,h (sum_j w_j c_j)
     linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
     linear(c, c->A, H * V, L.o, c->Y, E, T);
@@ -546,8 +610,9 @@ void stack_ctx_free(StackCtx * c) {
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->g_token) cudaGraphExecDestroy(c->g_token);
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
-    for (float * p : c->caches) cudaFree(p);
-    cudaFree(c->d_step); cudaFree(c->d_arg);
+    for (float * p : c->cache_allocs) cudaFree(p);
+    cudaFree(c->att_scores);
+    cudaFree(c->d_step); cudaFree(c->d_arg); cudaFree(c->att_part); cudaFree(c->att_ml);
     cudaFreeHost(c->h_step); cudaFreeHost(c->h_logits); cudaFreeHost(c->h_arg);
     if (c->ev0) { cudaEventDestroy(c->ev0); cudaEventDestroy(c->ev1); }
     if (c->st) cudaStreamDestroy(c->st);
@@ -562,23 +627,45 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
     try {
         SCU(cudaStreamCreateWithFlags(&c->st, cudaStreamNonBlocking));
         const size_t cap = (size_t) c->cap;
-        const auto fl = [&](float ** p, size_t n) { SCU(cudaMalloc(p, std::max<size_t>(n, 4) * 4)); };
+        // zero-filled: rows that a tile computes beyond the portion, and cached rows no token has written, must hold finite numbers
+        const auto fl = [&](float ** p, size_t n) { SCU(cudaMalloc(p, std::max<size_t>(n, 4) * 4)); SCU(cudaMemsetAsync(*p, 0, std::max<size_t>(n, 4) * 4, c->st)); };
+        const size_t cap_t = (cap + ATT_TQ - 1) / ATT_TQ * ATT_TQ;
         fl(&c->X, cap * m->E); fl(&c->Hn, cap * m->E); fl(&c->Y, cap * m->E);
-        fl(&c->P, cap * m->maxP); fl(&c->A, cap * m->maxA); fl(&c->QK, cap * m->maxQK); fl(&c->OL, cap * m->maxOL);
+        fl(&c->P, cap * m->maxP); fl(&c->A, cap * m->maxA); fl(&c->QK, cap_t * m->maxQK); fl(&c->OL, cap_t * m->maxOL);
         fl(&c->CV, cap * m->maxCV); fl(&c->BG, cap * m->maxBG); fl(&c->O, cap * m->maxA);
         fl(&c->rec, m->rec_floats);
         c->caches.assign((size_t) m->n_caches, nullptr);
-        size_t smem = 0;
+        cudaDeviceProp prop;
+        SCU(cudaGetDeviceProperties(&prop, m->device));
+        c->sm_count = prop.multiProcessorCount;
+        size_t smem = 0, part = 0, ml = 0;
         for (const LayerSpec & L : m->layers) {
             if (L.kind != MIX_LATENT) continue;
-            fl(&c->caches[(size_t) L.cache_index], (size_t) n_ctx * L.cache_row);
-            const size_t keys = (size_t) (L.window > 0 ? std::min(L.window, n_ctx) : n_ctx);
-            smem = std::max(smem, (L.cache_row + 16 + 256 + keys) * 4);
+            {   // [ window - 1 zero rows | n_ctx positions | one tile of slack ]: a tile's key range may start before position 0 and end past the portion
+                const size_t front = (size_t) std::max(L.window, 1), rows = front + (size_t) n_ctx + 2 * ATT_TQ;
+                float * base = nullptr;
+                fl(&base, rows * L.cache_row);
+                c->cache_allocs.push_back(base);
+                c->caches[(size_t) L.cache_index] = base + front * L.cache_row;
+                const size_t nk = (L.window > 0 ? (size_t) L.window + ATT_TQ - 1 : (size_t) n_ctx + ATT_TQ) + 3;
+                const size_t one = (size_t) ATT_TQ * L.H * nk;             // one tile's scores
+                const size_t all = (cap_t / ATT_TQ) * one;
+                c->att_scores_floats = std::max(c->att_scores_floats, std::min(all, std::max(one, ATT_SCORE_BYTES / 4)));
+            }
+            for (int T = 1; T <= c->cap; T++) {           // every pass size has its plan: the buffers cover the largest
+                const AttnPlan ap = plan_attention(L, n_ctx, T, c->sm_count);
+                smem = std::max(smem, ap.smem);
+                if (ap.nsplit > 1) { part = std::max(part, (size_t) T * L.H * ap.nsplit * L.rank); ml = std::max(ml, (size_t) T * L.H * ap.nsplit * 2); }
+            }
         }
-        if (smem > 227 * 1024) throw std::runtime_error("latent attention: the window (or an unmasked context) of " + std::to_string((smem / 4)) +
-                                                        " scores exceeds one block's shared memory; use a smaller n_ctx");
+        if (smem > 227 * 1024) throw std::runtime_error("latent attention: a context of " + std::to_string(n_ctx) + " positions without a window does not fit one block's shared memory; use a smaller n_ctx");
         c->attn_smem = smem;
-        if (smem > 48 * 1024) SCU(cudaFuncSetAttribute(k_latent_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        fl(&c->att_part, part); fl(&c->att_ml, ml);
+        if (c->att_scores_floats) fl(&c->att_scores, c->att_scores_floats);
+        {   // the opt-in limit is a property of the kernel, not of a context: it only ever grows
+            static size_t attr = 48 * 1024;
+            if (smem > attr) { SCU(cudaFuncSetAttribute(k_latent_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); attr = smem; }
+        }
         SCU(cudaMalloc(&c->d_step, sizeof(StepDev)));
         SCU(cudaMemsetAsync(c->d_step, 0, sizeof(StepDev), c->st));
         SCU(cudaMallocHost(&c->h_step, sizeof(StepDev)));

@@ -114,6 +114,7 @@ struct LinArgs {
     int vec;            // 1: K, ldx and all bases allow 16-byte loads
     int glu;            // 1: rows of W are interleaved (2i: gate_i, 2i + 1: up_i); the epilogue writes the clamped gated unit
     float limit, alpha; //    y_i = g sigmoid(alpha g) (u + 1), g = min(gate_i, limit), u = clamp(up_i, -limit, limit), to Y[t][i] (N / 2 wide)
+    int w_kn, ldw;      // w_kn = 1 (k_gemm_simt only): W is given [K][N] with row stride ldw (the attention's weights x cached rows)
 };
 __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
     const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
@@ -223,8 +224,15 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
             const int n = n0 + lr;
             float v[4] = { 0.f, 0.f, 0.f, 0.f };
             if (n < a.N) {
-                const size_t o = (size_t) n * a.K + k0 + lk;
-                for (int i = 0; i < 4; i++) if (k0 + lk + i < a.K) v[i] = wf(W, o + i);
+                if (a.w_kn) {
+                    for (int i = 0; i < 4; i++) if (k0 + lk + i < a.K) v[i] = wf(W, (size_t) (k0 + lk + i) * a.ldw + n);
+                } else {
+                    const size_t o = (size_t) n * a.K + k0 + lk;
+                    if (sizeof(WT) == 4 && a.vec && k0 + lk + 3 < a.K) {
+                        const float4 f = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(W) + o);
+                        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+                    } else for (int i = 0; i < 4; i++) if (k0 + lk + i < a.K) v[i] = wf(W, o + i);
+                }
             }
 #pragma unroll
             for (int i = 0; i < 4; i++) Ws[lk + i][lr] = v[i];
@@ -422,67 +430,169 @@ __global__ void k_latent_prep(const float * __restrict__ P, int ldp, int H, int 
 }
 
 // ---- latent attention, step 2: scores over the window, soft-max with a sink, weighted sum of the cached latents -------------------
-// One block per (token, head). Keys j with 0 <= p - j < window (window <= 0: every earlier position). The score of key j is
-// (QK[t][h] . cache[j]) * scale over all rank + R entries: the absorbed query against the latent plus the rotated parts. The
-// denominator also holds exp(sink[h]), which has no key and no value. OL[t][h] = sum_j w_j c_j (rank entries); the per-head
-// value matrix is applied afterwards (W_uv (sum_j w_j c_j) = sum_j w_j v_j).
-__global__ void __launch_bounds__(256) k_latent_attn(const float * __restrict__ QK, const float * __restrict__ cache, int H, int rank, int R, int window,
-                                                     float scale, const float * __restrict__ sink, const StepState * __restrict__ st, float * __restrict__ OL) {
+// Keys j with 0 <= p - j < window (window <= 0: every earlier position). The score of key j is (QK[t][h] . cache[j]) * scale
+// over all rank + R entries: the absorbed query against the latent plus the rotated parts. The denominator also holds
+// exp(sink[h]), which has no key and no value. OL[t][h] = sum_j w_j c_j (rank entries); the per-head value matrix is applied
+// afterwards (W_uv (sum_j w_j c_j) = sum_j w_j v_j).
+// All heads share one cached row per key, and neighbouring tokens share almost all their keys: a block takes TQ consecutive
+// tokens x HQ heads (NQ = TQ HQ <= 16 queries) and one of `nsplit` slices of the tile's key range, so every cached row it
+// loads serves NQ queries. nsplit == 1: the block finishes its queries. nsplit > 1 (decode: few queries, many SMs): it
+// leaves the un-normalised sum and (max, sum of exponentials) of its slice; k_latent_combine merges the slices.
+struct LatAttnArgs {
+    const float * QK; const float * cache; const float * sink; const StepState * st;
+    float * OL;            // [T][H][rank]
+    float * part;          // [T][H][nsplit][rank]
+    float * ml;            // [T][H][nsplit][2]
+    int T, H, rank, R, window;
+    float scale;
+    int TQ, HQ, nsplit, smax;      // smax: score-row stride = the most keys one block can get
+};
+constexpr int LAT_NQ_MAX = 16, LAT_RPT = 2;
+__global__ void __launch_bounds__(256) k_latent_attn(const LatAttnArgs a) {
     extern __shared__ float sm[];
-    const int t = blockIdx.x, h = blockIdx.y, pos = st->pos0 + t;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int W = rank + R;
-    const int j0 = window > 0 ? max(0, pos - window + 1) : 0;
-    const int nk = pos - j0 + 1;
-    float * q = sm;                      // [W]
-    float * red = sm + W;                // [16]
-    float * part = red + 16;             // [256] partial sums of the weighted sum
-    float * s = part + 256;              // [nk]
-    const float * qrow = QK + ((size_t) t * H + h) * W;
-    for (int i = tid; i < W; i += 256) q[i] = qrow[i];
+    const int W = a.rank + a.R, NQ = a.TQ * a.HQ;
+    const int t0 = blockIdx.x * a.TQ, h0 = blockIdx.y * a.HQ, z = blockIdx.z;
+    const int nt = min(a.TQ, a.T - t0);
+    const int p_first = a.st->pos0 + t0, p_last = p_first + nt - 1;
+    const int jlo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    const int nkeys = p_last - jlo + 1;
+    const int chunk = (nkeys + a.nsplit - 1) / a.nsplit;
+    const int jb = jlo + z * chunk, je = min(jb + chunk, p_last + 1), nk = max(je - jb, 0);      // this block's keys [jb, je)
+    float * q = sm;                       // [NQ][W]
+    float * s = q + (size_t) NQ * W;      // [NQ][smax]
+    float * inv = s + (size_t) NQ * a.smax;   // [NQ] factor on the weighted sum
+    for (int i = tid; i < NQ * W; i += 256) {
+        const int qi = i / W, e = i % W, tq = qi / a.HQ, h = h0 + qi % a.HQ;
+        q[i] = (tq < nt && h < a.H) ? a.QK[((size_t) (t0 + tq) * a.H + h) * W + e] : 0.f;
+    }
     __syncthreads();
-    float mx = -INFINITY;
+    // scores: one warp per key, four queries at a time against the key row
     for (int j = warp; j < nk; j += 8) {
-        const float * c = cache + (size_t) (j0 + j) * W;
-        float a = 0.f;
-        for (int i = lane; i < W; i += 32) a = fmaf(q[i], c[i], a);
-        a = warp_sum(a) * scale;
-        if (lane == 0) s[j] = a;
-        mx = fmaxf(mx, a);
-    }
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    const float snk = sink ? sink[h] : -INFINITY;
-    mx = snk;
-    for (int i = 0; i < 8; i++) mx = fmaxf(mx, red[i]);
-    __syncthreads();
-    float sum = 0.f;
-    for (int j = tid; j < nk; j += 256) { const float e = expf(s[j] - mx); s[j] = e; sum += e; }
-    sum = warp_sum(sum);
-    if (lane == 0) red[8 + warp] = sum;
-    __syncthreads();
-    float den = sink ? expf(snk - mx) : 0.f;
-    for (int i = 0; i < 8; i++) den += red[8 + i];
-    const float inv = 1.0f / den;
-    // weighted sum: `lanes_r` threads across the latent entries, 256 / lanes_r groups across the keys
-    const int lanes_r = min(256, (rank + 31) / 32 * 32), ng = 256 / lanes_r;
-    const int g = tid / lanes_r, r0 = tid % lanes_r;
-    float * out = OL + ((size_t) t * H + h) * rank;
-    for (int rb = 0; rb < rank; rb += lanes_r) {
-        const int r = rb + r0;
-        float acc = 0.f;
-        if (g < ng && r < rank)
-            for (int j = g; j < nk; j += ng) acc = fmaf(s[j], cache[(size_t) (j0 + j) * W + r], acc);
-        if (ng == 1) { if (r < rank) out[r] = acc * inv; continue; }
-        if (g < ng) part[g * lanes_r + r0] = acc;
-        __syncthreads();
-        if (g == 0 && r < rank) {
-            float a = 0.f;
-            for (int i = 0; i < ng; i++) a += part[i * lanes_r + r0];
-            out[r] = a * inv;
+        const float * c = a.cache + (size_t) (jb + j) * W;
+        for (int qb = 0; qb < NQ; qb += 4) {
+            float acc[4] = { 0.f, 0.f, 0.f, 0.f };
+            for (int e = lane; e < W; e += 32) {
+                const float kv = c[e];
+#pragma unroll
+                for (int k = 0; k < 4; k++) if (qb + k < NQ) acc[k] = fmaf(q[(size_t) (qb + k) * W + e], kv, acc[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                if (qb + k >= NQ) continue;
+                const float v = warp_sum(acc[k]) * a.scale;
+                const int qi = qb + k, tq = qi / a.HQ, p = p_first + tq, key = jb + j;
+                const bool ok = tq < nt && h0 + qi % a.HQ < a.H && key <= p && (a.window <= 0 || p - key < a.window);
+                if (lane == 0) s[(size_t) qi * a.smax + j] = ok ? v : -INFINITY;
+            }
         }
-        __syncthreads();
     }
+    __syncthreads();
+    // soft-max per query: one warp per query
+    for (int qi = warp; qi < NQ; qi += 8) {
+        float * row = s + (size_t) qi * a.smax;
+        const int tq = qi / a.HQ, h = h0 + qi % a.HQ;
+        const bool live = tq < nt && h < a.H;
+        float mx = -INFINITY;
+        for (int j = lane; j < nk; j += 32) mx = fmaxf(mx, row[j]);
+        mx = warp_max(mx);
+        const float snk = (a.sink && live) ? a.sink[h] : -INFINITY;
+        const float m = a.nsplit == 1 ? fmaxf(mx, snk) : mx;
+        float sum = 0.f;
+        for (int j = lane; j < nk; j += 32) { const float e = m == -INFINITY ? 0.f : expf(row[j] - m); row[j] = e; sum += e; }
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            if (a.nsplit == 1) {
+                const float den = sum + (snk == -INFINITY ? 0.f : expf(snk - m));
+                inv[qi] = den > 0.f ? 1.0f / den : 0.f;
+            } else {
+                inv[qi] = 1.0f;
+                if (live) {
+                    float * o = a.ml + (((size_t) (t0 + tq) * a.H + h) * a.nsplit + z) * 2;
+                    o[0] = m; o[1] = sum;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // weighted sum of the latents: a thread owns LAT_RPT entries of the latent for all NQ queries
+    for (int rb = 0; rb < a.rank; rb += 256 * LAT_RPT) {
+        float acc[LAT_NQ_MAX][LAT_RPT];
+#pragma unroll
+        for (int qi = 0; qi < LAT_NQ_MAX; qi++)
+#pragma unroll
+            for (int k = 0; k < LAT_RPT; k++) acc[qi][k] = 0.f;
+        for (int j = 0; j < nk; j++) {
+            const float * c = a.cache + (size_t) (jb + j) * W + rb + tid;
+            float cv[LAT_RPT];
+#pragma unroll
+            for (int k = 0; k < LAT_RPT; k++) cv[k] = rb + tid + 256 * k < a.rank ? c[256 * k] : 0.f;
+#pragma unroll
+            for (int qi = 0; qi < LAT_NQ_MAX; qi++) {
+                if (qi < NQ) {
+                    const float w = s[(size_t) qi * a.smax + j];
+#pragma unroll
+                    for (int k = 0; k < LAT_RPT; k++) acc[qi][k] = fmaf(w, cv[k], acc[qi][k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int qi = 0; qi < LAT_NQ_MAX; qi++) {
+            if (qi >= NQ) continue;
+            const int tq = qi / a.HQ, h = h0 + qi % a.HQ;
+            if (tq >= nt || h >= a.H) continue;
+            const size_t th = (size_t) (t0 + tq) * a.H + h;
+            float * o = a.nsplit == 1 ? a.OL + th * a.rank : a.part + (th * a.nsplit + z) * a.rank;
+#pragma unroll
+            for (int k = 0; k < LAT_RPT; k++) {
+                const int r = rb + tid + 256 * k;
+                if (r < a.rank) o[r] = acc[qi][k] * inv[qi];
+            }
+        }
+    }
+}
+// merge of the key slices of one (token, head): weights exp(m_z - M) with M the largest maximum (the sink included)
+__global__ void k_latent_combine(const LatAttnArgs a) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t th = (size_t) t * a.H + h;
+    const float * ml = a.ml + th * a.nsplit * 2;
+    const float snk = a.sink ? a.sink[h] : -INFINITY;
+    float M = snk;
+    for (int z = 0; z < a.nsplit; z++) M = fmaxf(M, ml[2 * z]);
+    float den = snk == -INFINITY ? 0.f : expf(snk - M);
+    for (int z = 0; z < a.nsplit; z++) if (ml[2 * z] != -INFINITY) den += ml[2 * z + 1] * expf(ml[2 * z] - M);
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    for (int r = threadIdx.x; r < a.rank; r += blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < a.nsplit; z++)
+            if (ml[2 * z] != -INFINITY) acc = fmaf(a.part[(th * a.nsplit + z) * a.rank + r], expf(ml[2 * z] - M), acc);
+        a.OL[th * a.rank + r] = acc * inv;
+    }
+}
+
+// Prompt portions compute the same attention as two float32 products around a row soft-max (all on the CUDA cores: scores and
+// weights stay 32-bit): per tile of TQ tokens, S = QK_tile (TQ H rows) x cached rows [jlo, jlo + nk)^T, then this kernel, then
+// OL_tile = S x cached latents. Row (t, h) of tile i = t / TQ sees key jlo_i + n, jlo_i = pos0 + i TQ - window + 1 (window > 0)
+// or 0; keys outside 0 <= p - j < window (or j < 0) get weight 0. One warp per row; the sink joins maximum and denominator.
+__global__ void k_latent_softmax_rows(float * __restrict__ S, int n_rows, int H, int TQ, int nk, int window, const float * __restrict__ sink,
+                                      const StepState * __restrict__ st, float scale, int tile0) {
+    const int lane = threadIdx.x & 31, row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // row = (t - tile0 TQ) H + h
+    if (row >= n_rows) return;
+    const int tl = row / H, h = row % H, t = tile0 * TQ + tl, p = st->pos0 + t;
+    const int jlo = window > 0 ? st->pos0 + (t / TQ) * TQ - window + 1 : 0;
+    float * s = S + (size_t) row * nk;
+    // valid n: j = jlo + n in [max(0, p - window + 1), p]
+    const int n_lo = max(window > 0 ? p - window + 1 : 0, 0) - jlo, n_hi = p - jlo;         // inclusive
+    float mx = -INFINITY;
+    for (int n = n_lo + lane; n <= n_hi; n += 32) mx = fmaxf(mx, s[n] * scale);
+    mx = warp_max(mx);
+    const float snk = sink ? sink[h] : -INFINITY;
+    const float m = fmaxf(mx, snk);
+    float sum = 0.f;
+    for (int n = n_lo + lane; n <= n_hi; n += 32) sum += expf(s[n] * scale - m);
+    sum = warp_sum(sum);
+    const float inv = 1.0f / (sum + (sink ? expf(snk - m) : 0.f));
+    for (int n = lane; n < nk; n += 32) s[n] = (n >= n_lo && n <= n_hi) ? expf(s[n] * scale - m) * inv : 0.f;
 }
 
 // ---- gated delta rule --------------------------------------------------------------------------------------------------
