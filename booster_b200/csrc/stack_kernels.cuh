@@ -61,6 +61,7 @@ __global__ void k_embed_rows(const WT * __restrict__ embed, const int32_t * __re
 
 // ---- end of a sub-layer, fused: X[t] += norm(Y[t]) * w_post, then (w_next != nullptr) Hn[t] = norm(X[t]) * w_next, the input
 // norm of the sub-layer that follows. Same groups for both; one block per row, one warp per group.
+constexpr int POST_NPL = 16;       // elements per lane k_post_norm_add keeps in registers (groups of up to 512)
 __global__ void k_post_norm_add(const float * __restrict__ Y, const float * __restrict__ w_post, float * __restrict__ X,
                                 const float * __restrict__ w_next, float * __restrict__ Hn, int n, int groups, float eps) {
     const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, gs = n / groups;
@@ -68,6 +69,33 @@ __global__ void k_post_norm_add(const float * __restrict__ Y, const float * __re
         const size_t b = (size_t) row * n + (size_t) g * gs;
         const float * y = Y + b;
         float * x = X + b;
+        if (gs <= 32 * POST_NPL) {
+            // the group lives in registers: one round trip to memory instead of three dependent passes (a decode step is latency-bound)
+            float yv[POST_NPL], xv[POST_NPL];
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < POST_NPL; k++) {
+                const int i = lane + 32 * k;
+                yv[k] = i < gs ? y[i] : 0.f; xv[k] = i < gs ? x[i] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < POST_NPL; k++) ss = fmaf(yv[k], yv[k], ss);
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float) gs + eps);
+            float s2 = 0.f;
+#pragma unroll
+            for (int k = 0; k < POST_NPL; k++) {
+                const int i = lane + 32 * k;
+                if (i < gs) { xv[k] = xv[k] + yv[k] * r * w_post[g * gs + i]; x[i] = xv[k]; s2 = fmaf(xv[k], xv[k], s2); }
+            }
+            if (w_next) {
+                s2 = warp_sum(s2);
+                const float r2 = 1.0f / sqrtf(s2 / (float) gs + eps);
+#pragma unroll
+                for (int k = 0; k < POST_NPL; k++) { const int i = lane + 32 * k; if (i < gs) Hn[b + i] = xv[k] * r2 * w_next[g * gs + i]; }
+            }
+            continue;
+        }
         float ss = 0.f;
         for (int i = lane; i < gs; i += 32) ss = fmaf(y[i], y[i], ss);
         ss = warp_sum(ss);
@@ -562,11 +590,14 @@ __global__ void k_latent_combine(const LatAttnArgs a) {
     float den = snk == -INFINITY ? 0.f : expf(snk - M);
     for (int z = 0; z < a.nsplit; z++) if (ml[2 * z] != -INFINITY) den += ml[2 * z + 1] * expf(ml[2 * z] - M);
     const float inv = den > 0.f ? 1.0f / den : 0.f;
+    __shared__ float wz[64];            // nsplit <= 64
+    if (threadIdx.x < a.nsplit) wz[threadIdx.x] = ml[2 * threadIdx.x] != -INFINITY ? expf(ml[2 * threadIdx.x] - M) * inv : 0.f;
+    __syncthreads();
     for (int r = threadIdx.x; r < a.rank; r += blockDim.x) {
         float acc = 0.f;
-        for (int z = 0; z < a.nsplit; z++)
-            if (ml[2 * z] != -INFINITY) acc = fmaf(a.part[(th * a.nsplit + z) * a.rank + r], expf(ml[2 * z] - M), acc);
-        a.OL[th * a.rank + r] = acc * inv;
+#pragma unroll 8
+        for (int z = 0; z < a.nsplit; z++) acc = fmaf(a.part[(th * a.nsplit + z) * a.rank + r], wz[z], acc);     // empty slices wrote zeros
+        a.OL[th * a.rank + r] = acc;
     }
 }
 
