@@ -1,5 +1,5 @@
 # Top-level build of libbooster_b200.so (the product) — sm_100a only, in-tree so that it travels to the GPU box.
-NVCC      ?= nvcc
+NVCC      ?= $(shell command -v nvcc 2>/dev/null || echo /usr/local/cuda/bin/nvcc)
 ARCH      := -gencode arch=compute_100a,code=sm_100a
 NVCCFLAGS := $(ARCH) -O3 -std=c++17 -lineinfo -Xcompiler -fPIC,-Wall,-Wno-unused-function -Xptxas -v
 CSRC      := booster_b200/csrc
