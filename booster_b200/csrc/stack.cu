@@ -443,16 +443,18 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
         // prompt portion: scores, row soft-max and weighted sum as float32 products over tiles of ATT_TQ tokens x all heads
         const int TQ = ATT_TQ, M = TQ * H, ntile = (T + TQ - 1) / TQ;
         const int pos0 = c->h_step->st.pos0;                                       // of this pass (set by the step function before the launches)
-        const int nk = ((L.window > 0 ? L.window + TQ - 1 : pos0 + ntile * TQ) + 3) / 4 * 4;   // keys a tile's rows can see (unmasked: all so far), padded for 16-byte rows
+        // keys a tile's rows can see: the window (no wider than the sequence so far) plus the tile; unmasked: all so far. Padded for 16-byte rows
+        const int span = L.window > 0 ? std::min(L.window, pos0 + ntile * TQ) : 0;
+        const int nk = ((L.window > 0 ? span + TQ - 1 : pos0 + ntile * TQ) + 3) / 4 * 4;
         const int per_group = (int) std::max<size_t>(1, c->att_scores_floats / ((size_t) M * nk));
         for (int g0 = 0; g0 < ntile; g0 += per_group) {
             const int ng = std::min(per_group, ntile - g0);
-            const long long jlo = L.window > 0 ? (long long) pos0 + (long long) g0 * TQ - L.window + 1 : 0;     // may be negative: the cache has a zero margin in front
+            const long long jlo = L.window > 0 ? (long long) pos0 + (long long) g0 * TQ - span + 1 : 0;     // may be negative: the cache has a zero margin in front
             const float * keys = cache + jlo * W;
             const long long sK = L.window > 0 ? (long long) TQ * W : 0;
             gemm_f32(c, c->QK + (size_t) g0 * M * W, W, (long long) M * W, keys, 0, 0, sK, c->att_scores, nk, (long long) M * nk, M, nk, W, ng);
             const int rows = (std::min(T, (g0 + ng) * TQ) - g0 * TQ) * H;
-            k_latent_softmax_rows<<<(rows + 7) / 8, 256, 0, c->st>>>(c->att_scores, rows, H, TQ, nk, L.window, L.sink, &c->d_step->st, L.scale, g0);
+            k_latent_softmax_rows<<<(rows + 7) / 8, 256, 0, c->st>>>(c->att_scores, rows, H, TQ, nk, L.window, span, L.sink, &c->d_step->st, L.scale, g0);
             gemm_f32(c, c->att_scores, nk, (long long) M * nk, keys, 1, W, sK, c->OL + (size_t) g0 * M * rank, rank, (long long) M * rank, M, rank, nk, ng);
             c->launches++;
         }

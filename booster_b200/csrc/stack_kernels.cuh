@@ -403,12 +403,23 @@ __global__ void k_mingru_scan(const float * __restrict__ P, int T, int width, fl
     if (c >= width) return;
     float s = state[c];
     const int ld = 3 * width;
-    for (int t = 0; t < T; t++) {
-        const float * p = P + (size_t) t * ld;
-        const float z = sigmoidf_(p[c]), u = p[width + c];
-        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
-        s = (1.0f - z) * s + z * cand;
-        A[(size_t) t * width + c] = s * siluf_(p[2 * width + c]);
+    constexpr int TB = 8;                 // tokens whose inputs are fetched together: the walk itself is serial, its loads are not
+    for (int t0 = 0; t0 < T; t0 += TB) {
+        float zp[TB], up[TB], gp[TB];
+#pragma unroll
+        for (int i = 0; i < TB; i++) {
+            const float * p = P + (size_t) min(t0 + i, T - 1) * ld;
+            zp[i] = p[c]; up[i] = p[width + c]; gp[i] = p[2 * width + c];
+        }
+#pragma unroll
+        for (int i = 0; i < TB; i++) {
+            if (t0 + i < T) {
+                const float z = sigmoidf_(zp[i]), u = up[i];
+                const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+                s = (1.0f - z) * s + z * cand;
+                A[(size_t) (t0 + i) * width + c] = s * siluf_(gp[i]);
+            }
+        }
     }
     state[c] = s;
 }
@@ -603,14 +614,14 @@ __global__ void k_latent_combine(const LatAttnArgs a) {
 
 // Prompt portions compute the same attention as two float32 products around a row soft-max (all on the CUDA cores: scores and
 // weights stay 32-bit): per tile of TQ tokens, S = QK_tile (TQ H rows) x cached rows [jlo, jlo + nk)^T, then this kernel, then
-// OL_tile = S x cached latents. Row (t, h) of tile i = t / TQ sees key jlo_i + n, jlo_i = pos0 + i TQ - window + 1 (window > 0)
+// OL_tile = S x cached latents. Row (t, h) of tile i = t / TQ sees key jlo_i + n, jlo_i = pos0 + i TQ - span + 1 (window > 0)
 // or 0; keys outside 0 <= p - j < window (or j < 0) get weight 0. One warp per row; the sink joins maximum and denominator.
-__global__ void k_latent_softmax_rows(float * __restrict__ S, int n_rows, int H, int TQ, int nk, int window, const float * __restrict__ sink,
+__global__ void k_latent_softmax_rows(float * __restrict__ S, int n_rows, int H, int TQ, int nk, int window, int span, const float * __restrict__ sink,
                                       const StepState * __restrict__ st, float scale, int tile0) {
     const int lane = threadIdx.x & 31, row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // row = (t - tile0 TQ) H + h
     if (row >= n_rows) return;
     const int tl = row / H, h = row % H, t = tile0 * TQ + tl, p = st->pos0 + t;
-    const int jlo = window > 0 ? st->pos0 + (t / TQ) * TQ - window + 1 : 0;
+    const int jlo = window > 0 ? st->pos0 + (t / TQ) * TQ - span + 1 : 0;      // span = min(window, positions so far): the range the product covered
     float * s = S + (size_t) row * nk;
     // valid n: j = jlo + n in [max(0, p - window + 1), p]
     const int n_lo = max(window > 0 ? p - window + 1 : 0, 0) - jlo, n_hi = p - jlo;         // inclusive
@@ -679,7 +690,7 @@ template <int DMAX>
 __global__ void __launch_bounds__(128) k_delta_scan(const float * __restrict__ CV, int C, const float * __restrict__ BG, int T, int H, int KH, int D, int V,
                                                     float * __restrict__ S, float * __restrict__ O) {
     constexpr int TT = 8;
-    __shared__ float ks[TT][DMAX], qs[TT][DMAX];
+    __shared__ float ks[TT][DMAX], qs[TT][DMAX], bg[TT][2], vs[TT][128];
     const int h = blockIdx.x, col = blockIdx.y * blockDim.x + threadIdx.x, kh = h / (H / KH);
     const bool live = col < V;
     float s[DMAX];
@@ -695,12 +706,16 @@ __global__ void __launch_bounds__(128) k_delta_scan(const float * __restrict__ C
             qs[tt][d] = d < D ? cv[(size_t) kh * D + d] : 0.f;
             ks[tt][d] = d < D ? cv[(size_t) (KH + kh) * D + d] : 0.f;
         }
+        if (threadIdx.x < 2 * nt) bg[threadIdx.x >> 1][threadIdx.x & 1] = BG[(size_t) (t0 + (threadIdx.x >> 1)) * 2 * H + (threadIdx.x & 1) * H + h];
+        // this column's values of the tile, fetched together (the walk below is serial, its loads are not)
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) vs[tt][threadIdx.x] = (live && tt < nt) ? CV[(size_t) (t0 + tt) * C + (size_t) 2 * KH * D + (size_t) h * V + col] : 0.f;
         __syncthreads();
         if (!live) continue;
         for (int tt = 0; tt < nt; tt++) {
             const int t = t0 + tt;
-            const float beta = BG[(size_t) t * 2 * H + h], g = BG[(size_t) t * 2 * H + H + h];
-            const float v = CV[(size_t) t * C + (size_t) 2 * KH * D + (size_t) h * V + col];
+            const float beta = bg[tt][0], g = bg[tt][1];
+            const float v = vs[tt][threadIdx.x];
             float dot = 0.f;
 #pragma unroll
             for (int d = 0; d < DMAX; d++) { s[d] *= g; dot = fmaf(s[d], ks[tt][d], dot); }
