@@ -17,7 +17,7 @@ _lib = None
 # every symbol the two headers declare (tests check the .so exports exactly these)
 BRIDGE_SYMBOLS = ["init", "initContext", "doInference", "stopInference", "status", "promptEval",
                   "getPromptTokenCount", "timing", "getSeed"]
-B200_SYMBOLS = ["b200_last_error", "b200_device_count", "b200_version", "b200_model_load", "b200_model_load_dtype", "b200_decode_rows", "b200_stack_time_linear", "b200_model_free",
+B200_SYMBOLS = ["b200_last_error", "b200_device_count", "b200_version", "b200_model_load", "b200_model_load_dtype", "b200_decode_rows", "b200_stack_time_linear", "b200_stack_linear", "b200_model_free",
                 "b200_model_info", "b200_model_weight_bytes", "b200_ctx_new", "b200_ctx_free", "b200_n_ctx",
                 "b200_kv_clear", "b200_decode", "b200_generate_greedy", "b200_step_greedy", "b200_set_taps", "b200_get_tap",
                 "b200_timings", "b200_reset_timings", "b200_kernel_launches", "b200_last_device_ms", "b200_profile_token", "b200_profile_kind", "b200_trace_token", "b200_trace_phases", "b200_set_token_kernel", "b200_set_prefill_batch", "b200_set_prefill_mma", "b200_set_prefill_attn_batch", "b200_job_timing_us", "b200_comm_unique_id",
@@ -68,6 +68,7 @@ def lib() -> C.CDLL:
     sig("b200_model_load_dtype", vp, [cp, C.c_int, C.c_int, C.c_int, cp])
     sig("b200_decode_rows", C.c_int, [vp, i32p, C.c_int, C.c_int, i32p, C.c_int, f32p])
     sig("b200_stack_time_linear", C.c_float, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int])
+    sig("b200_stack_linear", C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, C.c_int, C.c_float, f32p])
     sig("b200_model_free", None, [vp])
     sig("b200_model_info", C.c_int, [vp, i32p])
     sig("b200_model_weight_bytes", C.c_int64, [vp])

@@ -2087,6 +2087,14 @@ extern "C" float b200_stack_time_linear(int device, int dtype, int T, int N, int
         return b200::stack_time_linear(device, dtype, T, N, K, reps);
     } catch (const std::exception & e) { set_err(e.what()); cudaGetLastError(); return -1.f; }
 }
+extern "C" int b200_stack_linear(int device, int dtype, int T, int N, int K, const float * x, const float * w, const float * bias, int glu, float limit, float * y) {
+    try {
+        require_gpu();
+        if (T <= 0 || N <= 0 || K <= 0 || !x || !w || !y || (dtype != 0 && dtype != 1) || (glu && N % 2)) throw std::runtime_error("bad arguments");
+        b200::stack_linear(device, dtype, T, N, K, x, w, bias, glu, limit, y);
+        return 0;
+    } catch (const std::exception & e) { cudaGetLastError(); return set_err(e.what()); }
+}
 extern "C" float b200_last_device_ms(const b200_ctx * c) { return c ? c->last_device_ms : 0.f; }
 
 // One token, un-graphed, with a CUDA-event pair around every launch on the engine's own stream:

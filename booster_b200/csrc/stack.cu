@@ -111,6 +111,9 @@ struct StackCtx {
     std::vector<float *> cache_allocs;    // the caches with their zero margins (caches[] point behind the front margin)
     float * att_part = nullptr, * att_ml = nullptr;   // key-slice partials of the latent attention (decode)
     int sm_count = 148;
+    __nv_bfloat16 * xb = nullptr;         // activations of a prompt pass rounded to bfloat16 (operand of the tcgen05 product)
+    size_t xb_elems = 0;
+    int * d_err = nullptr, * h_err = nullptr;   // raised by a kernel whose bounded wait ran out
     bool taps = false;
     std::vector<float> tap_data;
     int tap_T = 0;
@@ -337,8 +340,17 @@ bool mma_enabled() {
     return on;
 }
 
+bool umma_enabled() {
+    static const bool on = [] { const char * e = std::getenv("BOOSTER_B200_STACK_UMMA"); return !(e && e[0] == '0'); }();
+    return on;
+}
+// what the tcgen05 product needs beside its operands: room for the activations rounded to bfloat16 and the error flag its
+// bounded waits raise
+struct UmmaScratch { __nv_bfloat16 * xb = nullptr; size_t elems = 0; int * err = nullptr; };
+
 void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, int ldx, const void * W, const float * bias, float * Y, int ldy,
-               int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f) {
+               int T, int N, int K, int batch = 1, long long sX = 0, long long sW = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f,
+               const UmmaScratch * us = nullptr) {
     if (T <= 0 || N <= 0) return;
     LinArgs a{X, W, bias, Y, T, N, K, ldx, ldy, sX, sW, sY, 0, glu ? 1 : 0, glu_limit, GLU_ALPHA, 0, 0};
     const int vecw = dtype == STACK_F32 ? 4 : 8;
@@ -353,6 +365,14 @@ void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, 
             const dim3 grid((unsigned) ((N + 7) / 8), 1, (unsigned) batch);
             if (dtype == STACK_F32) k_gemv<float, 1><<<grid, 256, 0, st>>>(a); else k_gemv<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(a);
         }
+    } else if (dtype == STACK_BF16 && a.vec && us && us->xb && umma_enabled() && T >= 64 && N >= 128 && K >= 64 && (size_t) batch * T * K <= us->elems) {
+        // tensor memory path: activations to bfloat16 once, then tcgen05.mma over cp.async-fed stages
+        static const bool attr = [] { return cudaFuncSetAttribute(k_gemm_bf16_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, UM_SMEM) == cudaSuccess; }();
+        if (!attr) throw std::runtime_error("cannot reserve shared memory for k_gemm_bf16_umma");
+        k_to_bf16<<<dim3((unsigned) std::min((K + 255) / 256, 64), (unsigned) T, (unsigned) batch), 256, 0, st>>>(X, ldx, T, K, sX, us->xb, (long long) T * K);
+        const dim3 grid((unsigned) ((N + UM_BN - 1) / UM_BN), (unsigned) ((T + UM_BM - 1) / UM_BM), (unsigned) batch);
+        k_gemm_bf16_umma<<<grid, 256, UM_SMEM, st>>>(a, us->xb, (long long) T * K, us->err);
+        if (launches) (*launches)++;
     } else if (dtype == STACK_BF16 && a.vec && mma_enabled()) {
         const dim3 grid((unsigned) ((N + MM_BN - 1) / MM_BN), (unsigned) ((T + MM_BM - 1) / MM_BM), (unsigned) batch);
         k_gemm_bf16_mma<<<grid, 256, 0, st>>>(a);
@@ -364,7 +384,8 @@ void linear_on(cudaStream_t st, int dtype, int64_t * launches, const float * X, 
 }
 
 void linear(StackCtx * c, const float * X, int ldx, const DMat & W, float * Y, int ldy, int T, int batch = 1, long long sX = 0, long long sY = 0, bool glu = false, float glu_limit = 0.f) {
-    linear_on(c->st, c->m->dtype, &c->launches, X, ldx, W.w, W.bias, Y, ldy, T, W.N, W.K, batch, sX, (long long) W.N * W.K, sY, glu, glu_limit);
+    const UmmaScratch us{c->xb, c->xb_elems, c->d_err};
+    linear_on(c->st, c->m->dtype, &c->launches, X, ldx, W.w, W.bias, Y, ldy, T, W.N, W.K, batch, sX, (long long) W.N * W.K, sY, glu, glu_limit, &us);
 }
 
 // end of a sub-layer: X += norm(Y) * w_post; Hn = norm(X) * w_next when another sub-layer follows
@@ -614,6 +635,7 @@ void stack_ctx_free(StackCtx * c) {
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
     for (float * p : c->cache_allocs) cudaFree(p);
     cudaFree(c->att_scores);
+    cudaFree(c->xb); cudaFree(c->d_err); cudaFreeHost(c->h_err);
     cudaFree(c->d_step); cudaFree(c->d_arg); cudaFree(c->att_part); cudaFree(c->att_ml);
     cudaFreeHost(c->h_step); cudaFreeHost(c->h_logits); cudaFreeHost(c->h_arg);
     if (c->ev0) { cudaEventDestroy(c->ev0); cudaEventDestroy(c->ev1); }
@@ -636,6 +658,12 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         fl(&c->P, cap * m->maxP); fl(&c->A, cap * m->maxA); fl(&c->QK, cap_t * m->maxQK); fl(&c->OL, cap_t * m->maxOL);
         fl(&c->CV, cap * m->maxCV); fl(&c->BG, cap * m->maxBG); fl(&c->O, cap * m->maxA);
         fl(&c->rec, m->rec_floats);
+        if (m->dtype == STACK_BF16) {
+            c->xb_elems = cap * (size_t) std::max({ m->E, m->maxA, m->maxOL, m->maxP });
+            SCU(cudaMalloc(&c->xb, c->xb_elems * 2));
+        }
+        SCU(cudaMalloc(&c->d_err, 4)); SCU(cudaMemsetAsync(c->d_err, 0, 4, c->st));
+        SCU(cudaMallocHost(&c->h_err, 4)); *c->h_err = 0;
         c->caches.assign((size_t) m->n_caches, nullptr);
         cudaDeviceProp prop;
         SCU(cudaGetDeviceProperties(&prop, m->device));
@@ -763,8 +791,10 @@ void stack_decode(StackCtx * c, const int32_t * tokens, int n, int pos0, const i
             if (nr) { enqueue_head(c, nr, row_off); row_off += nr; }
         }
         if (row_off) SCU(cudaMemcpyAsync(c->h_logits, c->d_logits, (size_t) row_off * m.vocab * 4, cudaMemcpyDeviceToHost, c->st));
+        SCU(cudaMemcpyAsync(c->h_err, c->d_err, 4, cudaMemcpyDeviceToHost, c->st));
         SCU(cudaEventRecord(c->ev1, c->st));
         SCU(cudaStreamSynchronize(c->st));
+        if (*c->h_err) throw std::runtime_error("a tensor-core product gave up waiting for its pipeline (k_gemm_bf16_umma); the step's results are invalid");
         if (row_off) { c->d_last_row = row_off - 1; c->h_last = c->h_logits + (size_t) (row_off - 1) * m.vocab; }
     }
     cudaEventElapsedTime(&c->last_ms, c->ev0, c->ev1);
@@ -795,6 +825,7 @@ int32_t stack_argmax(StackCtx * c) {
 float stack_time_linear(int device, int dtype, int T, int N, int K, int reps) {
     SCU(cudaSetDevice(device));
     float * X = nullptr, * Y = nullptr; void * W = nullptr;
+    UmmaScratch us;
     cudaStream_t st = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     float ms = 0.f;
@@ -804,22 +835,55 @@ float stack_time_linear(int device, int dtype, int T, int N, int K, int reps) {
     try {
         SCU(cudaMalloc(&X, (size_t) T * K * 4)); SCU(cudaMalloc(&Y, (size_t) T * N * 4)); SCU(cudaMalloc(&W, wbytes * copies));
         SCU(cudaMemset(X, 0, (size_t) T * K * 4)); SCU(cudaMemset(W, 0, wbytes * copies));
+        us.elems = (size_t) T * K;
+        SCU(cudaMalloc(&us.xb, us.elems * 2)); SCU(cudaMalloc(&us.err, 4)); SCU(cudaMemset(us.err, 0, 4));
         SCU(cudaStreamCreate(&st)); SCU(cudaEventCreate(&e0)); SCU(cudaEventCreate(&e1));
-        for (int i = 0; i < 3; i++) linear_on(st, dtype, nullptr, X, K, (char *) W + wbytes * (size_t) (i % copies), nullptr, Y, N, T, N, K);
+        for (int i = 0; i < 3; i++) linear_on(st, dtype, nullptr, X, K, (char *) W + wbytes * (size_t) (i % copies), nullptr, Y, N, T, N, K, 1, 0, 0, 0, false, 0.f, &us);
         SCU(cudaStreamSynchronize(st));
         SCU(cudaEventRecord(e0, st));
-        for (int i = 0; i < reps; i++) linear_on(st, dtype, nullptr, X, K, (char *) W + wbytes * (size_t) (i % copies), nullptr, Y, N, T, N, K);
+        for (int i = 0; i < reps; i++) linear_on(st, dtype, nullptr, X, K, (char *) W + wbytes * (size_t) (i % copies), nullptr, Y, N, T, N, K, 1, 0, 0, 0, false, 0.f, &us);
         SCU(cudaEventRecord(e1, st));
         SCU(cudaStreamSynchronize(st));
         cudaEventElapsedTime(&ms, e0, e1);
     } catch (...) {
-        cudaFree(X); cudaFree(Y); cudaFree(W);
+        cudaFree(X); cudaFree(Y); cudaFree(W); cudaFree(us.xb); cudaFree(us.err);
         if (st) cudaStreamDestroy(st);
         throw;
     }
-    cudaFree(X); cudaFree(Y); cudaFree(W);
+    cudaFree(X); cudaFree(Y); cudaFree(W); cudaFree(us.xb); cudaFree(us.err);
     cudaEventDestroy(e0); cudaEventDestroy(e1); cudaStreamDestroy(st);
     return ms / (float) std::max(reps, 1);
+}
+
+void stack_linear(int device, int dtype, int T, int N, int K, const float * x, const float * w, const float * bias, int glu, float limit, float * y) {
+    SCU(cudaSetDevice(device));
+    StackModel tmp;                      // owns the device copies
+    tmp.device = device; tmp.dtype = dtype;
+    float * X = nullptr, * Y = nullptr;
+    UmmaScratch us;
+    int herr = 0;
+    const int ny = glu ? N / 2 : N;
+    try {
+        const std::vector<float> wv(w, w + (size_t) N * K);
+        std::vector<float> bv;
+        if (bias) bv.assign(bias, bias + N);
+        const DMat d = up_mat(tmp, wv, N, K, bias ? &bv : nullptr);
+        SCU(cudaMalloc(&X, (size_t) T * K * 4)); SCU(cudaMalloc(&Y, (size_t) T * ny * 4));
+        SCU(cudaMemcpy(X, x, (size_t) T * K * 4, cudaMemcpyHostToDevice));
+        us.elems = (size_t) T * K;
+        SCU(cudaMalloc(&us.xb, us.elems * 2)); SCU(cudaMalloc(&us.err, 4)); SCU(cudaMemset(us.err, 0, 4));
+        linear_on(nullptr, dtype, nullptr, X, K, d.w, d.bias, Y, ny, T, N, K, 1, 0, 0, 0, glu != 0, limit, &us);
+        SCU(cudaDeviceSynchronize());
+        SCU(cudaMemcpy(y, Y, (size_t) T * ny * 4, cudaMemcpyDeviceToHost));
+        SCU(cudaMemcpy(&herr, us.err, 4, cudaMemcpyDeviceToHost));
+    } catch (...) {
+        cudaFree(X); cudaFree(Y); cudaFree(us.xb); cudaFree(us.err);
+        for (void * p : tmp.allocs) cudaFree(p);
+        throw;
+    }
+    cudaFree(X); cudaFree(Y); cudaFree(us.xb); cudaFree(us.err);
+    for (void * p : tmp.allocs) cudaFree(p);
+    if (herr) throw std::runtime_error("k_gemm_bf16_umma gave up waiting for its pipeline");
 }
 
 }  // namespace b200

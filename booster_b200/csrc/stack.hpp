@@ -48,5 +48,8 @@ float   stack_last_device_ms(const StackCtx * c);
 
 // micro-benchmark of one product shape through the family's own kernels (bench.py): ms per call, CUDA events
 float   stack_time_linear(int device, int dtype, int T, int N, int K, int reps);
+// one product y[T][N] = x[T][K] w[N][K]^T (+ bias; glu: rows of w interleaved gate/up, y[T][N/2] = the clamped gated unit)
+// through the kernel the family would pick for that shape (parity tests)
+void    stack_linear(int device, int dtype, int T, int N, int K, const float * x, const float * w, const float * bias, int glu, float limit, float * y);
 
 }  // namespace b200

@@ -395,6 +395,166 @@ __global__ void __launch_bounds__(256) k_gemm_bf16_mma(const LinArgs a) {
             }
 }
 
+// ---- prompt portions with bfloat16 weights on the 5th-generation tensor cores -------------------------------------------------
+// tcgen05.mma (kind::f16, bf16 x bf16 -> f32) with the accumulator in tensor memory: D[128 tokens][256 rows of W] per CTA.
+//   operands   both K-major in the canonical no-swizzle core-matrix order [8-row group][k-chunk][8 rows][16 B]: a 16-byte
+//              cp.async per (row, k-chunk) drops global rows straight into that order (zero-fill past T, N or K), four stages of
+//              K = 64 deep; the activations were rounded to bfloat16 by k_to_bf16 beforehand
+//   issue      one thread: four K = 16 MMAs per stage, tcgen05.commit -> the stage's mbarrier (frees the stage for the refill)
+//   epilogue   warp w owns TMEM lanes 32 (w & 3) .. + 31 (= tokens) and column half w >> 2: tcgen05.ld, bias / gated unit, stores
+// Every wait on an mbarrier is bounded: on a timeout the CTA raises *err, skips what is left and still frees its tensor memory.
+__global__ void k_to_bf16(const float * __restrict__ X, int ldx, int T, int K, long long sX, __nv_bfloat16 * __restrict__ Xb, long long sXb) {
+    const float * x = X + (size_t) blockIdx.z * sX + (size_t) blockIdx.y * ldx;
+    __nv_bfloat16 * o = Xb + (size_t) blockIdx.z * sXb + (size_t) blockIdx.y * K;
+    for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < K; k += gridDim.x * blockDim.x) o[k] = __float2bfloat16_rn(x[k]);
+}
+constexpr int UM_BM = 128, UM_BN = 256, UM_BK = 64, UM_STAGES = 4;
+constexpr int UM_A_BYTES = UM_BM * UM_BK * 2, UM_B_BYTES = UM_BN * UM_BK * 2, UM_STAGE_BYTES = UM_A_BYTES + UM_B_BYTES;
+constexpr int UM_SMEM = UM_STAGES * UM_STAGE_BYTES + 1024;                 // + alignment slack
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void * src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int * failed, int * err) {
+    if (*failed) return false;
+    for (uint32_t spins = 0; spins < (1u << 22); spins++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    *failed = 1;
+    atomicExch(err, 1);
+    return false;
+}
+__global__ void __launch_bounds__(256, 1) k_gemm_bf16_umma(const LinArgs a, const __nv_bfloat16 * __restrict__ Xb, long long sXb, int * err) {
+    extern __shared__ uint8_t um_raw[];
+    __shared__ __align__(8) uint64_t done[UM_STAGES];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int failed_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t smem0 = (smem_addr(um_raw) + 1023u) & ~1023u;
+    const int m0 = blockIdx.y * UM_BM, n0 = blockIdx.x * UM_BN;
+    const __nv_bfloat16 * X = Xb + (size_t) blockIdx.z * sXb;
+    const __nv_bfloat16 * W = reinterpret_cast<const __nv_bfloat16 *>(a.W) + (size_t) blockIdx.z * a.sW;
+    volatile int * failed = &failed_s;
+    if (tid == 0) {
+        failed_s = 0;
+        for (int s = 0; s < UM_STAGES; s++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_addr(&done[s])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_addr(&tmem_base_s)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_base_s;
+    const int nk = (a.K + UM_BK - 1) / UM_BK;
+    // one stage: 128 x 8 chunks of A (4 per thread) and 256 x 8 chunks of B (8 per thread); a warp's 32 chunks are 512 contiguous bytes
+    const auto issue_copies = [&](int kt, int slot) {
+        const uint32_t sa = smem0 + (uint32_t) slot * UM_STAGE_BYTES, sb = sa + UM_A_BYTES;
+        const int k0 = kt * UM_BK;
+#pragma unroll
+        for (int i = 0; i < 12; i++) {
+            const int idx = tid + 256 * (i < 4 ? i : i - 4);
+            const int r_in = idx & 7, kc = (idx >> 3) & 7, rg = idx >> 6;
+            const int k = k0 + kc * 8;
+            const uint32_t off = (uint32_t) rg * 1024u + (uint32_t) kc * 128u + (uint32_t) r_in * 16u;
+            if (i < 4) {
+                const int m = m0 + rg * 8 + r_in;
+                const bool ok = m < a.T && k < a.K;
+                cp_async16(sa + off, ok ? (const void *) (X + (size_t) m * a.K + k) : (const void *) X, ok ? 16u : 0u);
+            } else {
+                const int n = n0 + rg * 8 + r_in;
+                const bool ok = n < a.N && k < a.K;
+                cp_async16(sb + off, ok ? (const void *) (W + (size_t) n * a.K + k) : (const void *) W, ok ? 16u : 0u);
+            }
+        }
+    };
+    for (int s = 0; s < UM_STAGES - 1; s++) {
+        if (s < nk) issue_copies(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    // instruction descriptor: D f32, A and B bf16, both K-major, N = 256, M = 128
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (UM_BN >> 3) << 17) | ((uint32_t) (UM_BM >> 4) << 24);
+    for (int kt = 0; kt < nk; kt++) {
+        const int slot = kt % UM_STAGES;
+        asm volatile("cp.async.wait_group %0;" :: "n"(UM_STAGES - 2) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");          // the copies' writes -> visible to the tensor core's reads
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0 && !*failed) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t sa = smem0 + (uint32_t) slot * UM_STAGE_BYTES, sb = sa + UM_A_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < UM_BK / 16; ks++) {
+                // K-major, no swizzle: start >> 4 | (k-chunk stride 128 B) >> 4 << 16 | (8-row group stride 1024 B) >> 4 << 32 | version 1
+                const uint64_t da = (uint64_t) (((sa + ks * 256u) >> 4) & 0x3fffu) | ((uint64_t) (128u >> 4) << 16) | ((uint64_t) (1024u >> 4) << 32) | (1ull << 46);
+                const uint64_t db = (uint64_t) (((sb + ks * 256u) >> 4) & 0x3fffu) | ((uint64_t) (128u >> 4) << 16) | ((uint64_t) (1024u >> 4) << 32) | (1ull << 46);
+                const uint32_t accumulate = (kt | ks) ? 1u : 0u;
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                             :: "r"(tmem), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate) : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_addr(&done[slot])) : "memory");
+        }
+        // refill the slot of stage kt - 1 with stage kt + STAGES - 1 once its MMAs have read it
+        const int nxt = kt + UM_STAGES - 1;
+        if (nxt < nk) {
+            if (kt >= 1) mbar_wait_limited(smem_addr(&done[(kt - 1) % UM_STAGES]), (uint32_t) (((kt - 1) / UM_STAGES) & 1), failed, err);
+            if (!*failed) issue_copies(nxt, nxt % UM_STAGES);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const bool ok = mbar_wait_limited(smem_addr(&done[(nk - 1) % UM_STAGES]), (uint32_t) (((nk - 1) / UM_STAGES) & 1), failed, err);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+        const int m = m0 + 32 * (warp & 3) + lane, cbase = (warp >> 2) * (UM_BN / 2);
+        const uint32_t taddr = tmem + ((uint32_t) (32 * (warp & 3)) << 16) + (uint32_t) cbase;
+        float * Y = a.Y + (size_t) blockIdx.z * a.sY + (size_t) m * a.ldy;
+#pragma unroll 1
+        for (int c = 0; c < UM_BN / 2; c += 16) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t r0, r1, r2, r3;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr + (uint32_t) (c + 4 * j)) : "memory");
+                v[4 * j] = __uint_as_float(r0); v[4 * j + 1] = __uint_as_float(r1); v[4 * j + 2] = __uint_as_float(r2); v[4 * j + 3] = __uint_as_float(r3);
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (m < a.T) {
+                const int nb = n0 + cbase + c;
+                if (!a.glu && nb + 15 < a.N && (a.ldy & 3) == 0 && ((uintptr_t) (Y + nb) & 15) == 0) {       // whole 16-byte stores
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        if (a.bias) { o.x += a.bias[nb + j]; o.y += a.bias[nb + j + 1]; o.z += a.bias[nb + j + 2]; o.w += a.bias[nb + j + 3]; }
+                        *reinterpret_cast<float4 *>(Y + nb + j) = o;
+                    }
+                    continue;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const int n = n0 + cbase + c + j;
+                    if (a.glu) {
+                        if (n + 1 < a.N) Y[n >> 1] = clamped_glu(v[j] + (a.bias ? a.bias[n] : 0.f), v[j + 1] + (a.bias ? a.bias[n + 1] : 0.f), a.limit, a.alpha);
+                    } else {
+                        if (n < a.N) Y[n] = v[j] + (a.bias ? a.bias[n] : 0.f);
+                        if (n + 1 < a.N) Y[n + 1] = v[j + 1] + (a.bias ? a.bias[n + 1] : 0.f);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(256u) : "memory");
+    }
+}
+
 // ---- minGRU: S_t = (1 - z) S_(t-1) + z * cand, gates from the current token only ----------------------------------------
 // P[t] = [ z pre-activation | candidate pre-activation u | output-gate pre-activation ] (3 * width, biases included);
 // cand = u + 1/2 for u >= 0, sigmoid(u) below. A[t] = S_t * silu(gate). One thread per channel walks the portion in order.

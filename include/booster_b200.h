@@ -123,6 +123,12 @@ void b200_reset_timings(b200_ctx * c);
  * T <= 4 takes the decode mat-vec, larger T the prompt kernels), CUDA events around `reps` launches over distinct weights;
  * negative on error. bench.py's per-kernel roofline of the family. */
 float b200_stack_time_linear(int device, int dtype, int T, int N, int K, int reps);
+/* operator-level parity entry of the same products: y[T][N] = x[T][K] . w[N][K]^T (+ bias[N]); glu != 0: the rows of w are
+ * interleaved (gate_i, up_i) and y is [T][N / 2], the clamped gated unit g sigmoid(1.702 g) (u + 1) with g = min(gate, limit),
+ * u = clamp(up, +-limit). Host pointers; w is rounded to bfloat16 when dtype = 0. The shape picks the kernel as in serving:
+ * T <= 4 the mat-vec, else (bfloat16) tcgen05.mma with TMEM accumulators for T >= 64, N >= 128, K >= 64, K % 8 == 0, mma.sync
+ * for other 16-byte-aligned shapes, the CUDA-core product for float32 and odd shapes. */
+int b200_stack_linear(int device, int dtype, int T, int N, int K, const float * x, const float * w, const float * bias, int glu, float limit, float * y);
 /* number of kernels launched by this library's own code since the context was created */
 int64_t b200_kernel_launches(const b200_ctx * c);
 /* device time (CUDA events on the engine's stream) of the last b200_generate_greedy /

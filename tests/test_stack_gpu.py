@@ -5,6 +5,7 @@ odd sizes (vector and scalar load paths, grouped key heads, one norm group, part
 generation through the bridge's job loop. Small random models written to a temporary folder; float32 is the sharp
 comparison."""
 import copy
+import ctypes as C
 import os
 
 import numpy as np
@@ -319,3 +320,32 @@ def test_bad_models_fail_loudly(tmp_path):
     with pytest.raises(_lib.B200Error, match="not available"):
         c.kv_seq_rm(0, 1)
     c.close(); m.close()
+
+
+@pytest.mark.parametrize("dtype,T,N,K,glu", [
+    ("bfloat16", 1, 70, 48, False), ("bfloat16", 4, 66, 36, True),            # mat-vec: vector and scalar loads
+    ("bfloat16", 37, 100, 64, False), ("bfloat16", 21, 64, 40, True),         # mma.sync
+    ("bfloat16", 200, 300, 136, False), ("bfloat16", 130, 512, 64, True),     # tcgen05 + TMEM: ragged and whole tiles
+    ("bfloat16", 513, 258, 1032, False),                                      # more K steps than pipeline stages, several token tiles
+    ("bfloat16", 70, 130, 35, False),                                         # odd K: CUDA cores
+    ("float32", 50, 70, 33, True), ("float32", 3, 9, 7, False)], ids=str)
+def test_products_pick_their_kernel_and_agree_with_numpy(dtype, T, N, K, glu):
+    rng = np.random.default_rng(T * 1000 + N)
+    x = rng.standard_normal((T, K)).astype(np.float32)
+    w = so.round_bf16(rng.standard_normal((N, K)).astype(np.float32) / np.sqrt(K))
+    b = so.round_bf16(rng.standard_normal(N).astype(np.float32))
+    limit = 0.8
+    y = np.zeros((T, N // 2 if glu else N), np.float32)
+    f32p = C.POINTER(C.c_float)
+    L = _lib.lib()
+    rc = L.b200_stack_linear(0, 0 if dtype == "bfloat16" else 1, T, N, K, x.ctypes.data_as(f32p), w.ctypes.data_as(f32p), b.ctypes.data_as(f32p),
+                             int(glu), limit, y.ctypes.data_as(f32p))
+    assert rc == 0, _lib.last_error()
+    # the tensor-core paths round the activations to bfloat16; everything else keeps them in float32
+    tensor = dtype == "bfloat16" and T > 4 and K % 8 == 0
+    xe = so.round_bf16(x) if tensor else x
+    ref = xe.astype(np.float64) @ w.astype(np.float64).T + b
+    if glu:
+        g, u = np.minimum(ref[:, 0::2], limit), np.clip(ref[:, 1::2], -limit, limit)
+        ref = g * so.sigmoid(1.702 * g) * (u + 1.0)
+    assert np.abs(y - ref).max() < 2e-5 * max(1.0, np.abs(ref).max()) * np.sqrt(K)
