@@ -165,31 +165,44 @@ __global__ void __launch_bounds__(256) k_gemv(const LinArgs a) {
         for (int t = 0; t < GEMV_MAX_T; t++) acc[r][t] = 0.f;
     constexpr int VEC = 16 / (int) sizeof(WT);
     if (a.vec) {
-        for (int k = lane * VEC; k < a.K; k += 32 * VEC) {
-            float wv[RPW][VEC];
+        // U chunks of 16 bytes per row and lane are requested before any is used: a mat-vec is bound by the bytes in flight
+        constexpr int U = RPW == 2 ? 2 : 4;
+        for (int kb = lane * VEC; kb < a.K; kb += 32 * VEC * U) {
+            uint4 raw[RPW][U];
 #pragma unroll
-            for (int r = 0; r < RPW; r++) {
-                if constexpr (sizeof(WT) == 2) {
-                    const uint4 u = *reinterpret_cast<const uint4 *>(w + (size_t) r * a.K + k);
-                    const uint32_t uu[4] = { u.x, u.y, u.z, u.w };
+            for (int u = 0; u < U; u++) {
+                const int k = kb + u * 32 * VEC;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) { wv[r][2 * i] = __uint_as_float(uu[i] << 16); wv[r][2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u); }
-                } else {
-                    const float4 f = *reinterpret_cast<const float4 *>(w + (size_t) r * a.K + k);
-                    wv[r][0] = f.x; wv[r][1] = f.y; wv[r][2] = f.z; wv[r][3] = f.w;
-                }
+                for (int r = 0; r < RPW; r++) raw[r][u] = k < a.K ? *reinterpret_cast<const uint4 *>(w + (size_t) r * a.K + k) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
-            for (int t = 0; t < GEMV_MAX_T; t++) {
-                if (t < a.T) {
-                    const float * xt = x + (size_t) t * a.ldx + k;
+            for (int u = 0; u < U; u++) {
+                const int k = kb + u * 32 * VEC;
+                if (k >= a.K) break;
+                float wv[RPW][VEC];
 #pragma unroll
-                    for (int i = 0; i < VEC; i += 4) {
-                        const float4 xv = *reinterpret_cast<const float4 *>(xt + i);
+                for (int r = 0; r < RPW; r++) {
+                    const uint32_t uu[4] = { raw[r][u].x, raw[r][u].y, raw[r][u].z, raw[r][u].w };
+                    if constexpr (sizeof(WT) == 2) {
 #pragma unroll
-                        for (int r = 0; r < RPW; r++) {
-                            acc[r][t] = fmaf(wv[r][i], xv.x, acc[r][t]); acc[r][t] = fmaf(wv[r][i + 1], xv.y, acc[r][t]);
-                            acc[r][t] = fmaf(wv[r][i + 2], xv.z, acc[r][t]); acc[r][t] = fmaf(wv[r][i + 3], xv.w, acc[r][t]);
+                        for (int i = 0; i < 4; i++) { wv[r][2 * i] = __uint_as_float(uu[i] << 16); wv[r][2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u); }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) wv[r][i] = __uint_as_float(uu[i]);
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < GEMV_MAX_T; t++) {
+                    if (t < a.T) {
+                        const float * xt = x + (size_t) t * a.ldx + k;
+#pragma unroll
+                        for (int i = 0; i < VEC; i += 4) {
+                            const float4 xv = *reinterpret_cast<const float4 *>(xt + i);
+#pragma unroll
+                            for (int r = 0; r < RPW; r++) {
+                                acc[r][t] = fmaf(wv[r][i], xv.x, acc[r][t]); acc[r][t] = fmaf(wv[r][i + 1], xv.y, acc[r][t]);
+                                acc[r][t] = fmaf(wv[r][i + 2], xv.z, acc[r][t]); acc[r][t] = fmaf(wv[r][i + 3], xv.w, acc[r][t]);
+                            }
                         }
                     }
                 }
