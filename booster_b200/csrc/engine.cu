@@ -1986,14 +1986,8 @@ extern "C" int b200_generate_greedy(b200_ctx * c, int32_t first_token, int pos0,
         b200_model & m = *c->m;
         if (c->stack) {                 // one graph replay + device arg-max per token
             if (!out_tokens) throw std::runtime_error("null output");
-            float ms = 0.f;
-            int32_t tok = first_token;
-            for (int i = 0; i < n_steps; i++) {
-                b200::stack_decode(c->stack, &tok, 1, pos0 + i, nullptr, 1, nullptr);
-                ms += b200::stack_last_device_ms(c->stack);
-                out_tokens[i] = tok = b200::stack_argmax(c->stack);
-            }
-            c->last_device_ms = ms;
+            b200::stack_generate_greedy(c->stack, first_token, pos0, n_steps, out_tokens);
+            c->last_device_ms = b200::stack_last_device_ms(c->stack);
             c->n_gen += n_steps;
             return 0;
         }

@@ -103,6 +103,9 @@ struct StackCtx {
     int64_t d_last_row = -1;              // its row in d_logits
     int32_t * d_arg = nullptr, * h_arg = nullptr;
     cudaGraphExec_t g_token = nullptr;    // one token: header in -> layers -> head -> logits out
+    cudaGraphExec_t g_greedy = nullptr;   // one token of the device-resident greedy loop: layers -> head -> arg-max -> next header
+    int64_t n_greedy_launches = 0;
+    int32_t * d_out_tokens = nullptr, * d_counter = nullptr;
     bool graph_failed = false;
     int64_t n_token_launches = 0;         // kernels per replay of g_token
     size_t attn_smem = 0;                 // the most dynamic shared memory any attention launch of this context asks for
@@ -561,7 +564,8 @@ void ensure_logit_rows(StackCtx * c, int64_t rows) {
     cudaFreeHost(c->h_logits);
     c->d_logits = d; c->h_logits = h; c->logit_rows_cap = cap;
     c->h_last = nullptr; c->d_last_row = -1;
-    if (c->g_token) { cudaGraphExecDestroy(c->g_token); c->g_token = nullptr; }      // it holds the old addresses
+    if (c->g_token) { cudaGraphExecDestroy(c->g_token); c->g_token = nullptr; }      // they hold the old addresses
+    if (c->g_greedy) { cudaGraphExecDestroy(c->g_greedy); c->g_greedy = nullptr; }
 }
 
 bool graph_enabled() {
@@ -632,6 +636,8 @@ void stack_ctx_free(StackCtx * c) {
     cudaSetDevice(c->m->device);
     if (c->st) cudaStreamSynchronize(c->st);
     if (c->g_token) cudaGraphExecDestroy(c->g_token);
+    if (c->g_greedy) cudaGraphExecDestroy(c->g_greedy);
+    cudaFree(c->d_out_tokens); cudaFree(c->d_counter);
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
     for (float * p : c->cache_allocs) cudaFree(p);
     cudaFree(c->att_scores);
@@ -700,6 +706,7 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         SCU(cudaMemsetAsync(c->d_step, 0, sizeof(StepDev), c->st));
         SCU(cudaMallocHost(&c->h_step, sizeof(StepDev)));
         std::memset(c->h_step, 0, sizeof(StepDev));
+        SCU(cudaMalloc(&c->d_out_tokens, (size_t) (n_ctx + 1) * 4)); SCU(cudaMalloc(&c->d_counter, 4));
         SCU(cudaMalloc(&c->d_arg, 4));
         SCU(cudaMallocHost(&c->h_arg, 4));
         SCU(cudaEventCreate(&c->ev0)); SCU(cudaEventCreate(&c->ev1));
@@ -802,12 +809,71 @@ void stack_decode(StackCtx * c, const int32_t * tokens, int n, int pos0, const i
     if (logits_out && n_rows > 0) std::memcpy(logits_out, c->h_logits, (size_t) n_rows * m.vocab * 4);
 }
 
+// Device-resident greedy loop: token -> layers -> head -> arg-max -> next token, n_steps times, one graph replay per token and
+// no host round trip in between; out_tokens[n_steps] receives the ids.
+void stack_generate_greedy(StackCtx * c, int32_t first_token, int pos0, int n_steps, int32_t * out_tokens) {
+    StackModel & m = *c->m;
+    if (n_steps <= 0 || !out_tokens) throw std::runtime_error("bad arguments");
+    if (pos0 != c->n_past) throw std::runtime_error("the burst must continue the sequence at position " + std::to_string(c->n_past));
+    if ((int64_t) pos0 + n_steps > c->n_ctx) throw std::runtime_error("the burst exceeds the context of " + std::to_string(c->n_ctx) + " positions");
+    if (first_token < 0 || first_token >= m.vocab) throw std::runtime_error("token id outside the vocabulary");
+    if (c->taps || !graph_enabled() || c->graph_failed) {
+        int32_t tok = first_token;
+        float ms = 0.f;
+        for (int i = 0; i < n_steps; i++) { stack_decode(c, &tok, 1, pos0 + i, nullptr, 1, nullptr); ms += c->last_ms; out_tokens[i] = tok = stack_argmax(c); }
+        c->last_ms = ms;
+        return;
+    }
+    SCU(cudaSetDevice(m.device));
+    ensure_logit_rows(c, 1);
+    SCU(cudaStreamSynchronize(c->st));
+    c->h_step->st.pos0 = pos0; c->h_step->st.n_tokens = 1; c->h_step->tokens[0] = first_token;
+    const auto body = [&]() {
+        enqueue_layers(c, 1);
+        enqueue_head(c, 1, 0);
+        k_argmax_advance<<<1, 1024, 0, c->st>>>(c->d_logits, m.vocab, &c->d_step->st, c->d_step->tokens, c->d_out_tokens, c->d_counter);
+        c->launches++;
+    };
+    if (!c->g_greedy) {
+        const int64_t before = c->launches;
+        cudaGraph_t g = nullptr;
+        bool ok = cudaStreamBeginCapture(c->st, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if (ok) {
+            try { body(); } catch (...) { ok = false; }
+            if (cudaStreamEndCapture(c->st, &g) != cudaSuccess) ok = false;
+        }
+        if (ok && cudaGraphInstantiate(&c->g_greedy, g, 0) != cudaSuccess) { ok = false; c->g_greedy = nullptr; }
+        if (g) cudaGraphDestroy(g);
+        c->n_greedy_launches = c->launches - before;
+        c->launches = before;
+        if (!ok) { cudaGetLastError(); c->graph_failed = true; stack_generate_greedy(c, first_token, pos0, n_steps, out_tokens); return; }
+    }
+    SCU(cudaMemcpyAsync(c->d_step, c->h_step, sizeof(StepState) + sizeof(int32_t), cudaMemcpyHostToDevice, c->st));
+    SCU(cudaMemsetAsync(c->d_step->rows, 0, sizeof(int32_t), c->st));
+    SCU(cudaMemsetAsync(c->d_counter, 0, 4, c->st));
+    SCU(cudaEventRecord(c->ev0, c->st));
+    for (int i = 0; i < n_steps; i++) SCU(cudaGraphLaunch(c->g_greedy, c->st));
+    SCU(cudaEventRecord(c->ev1, c->st));
+    SCU(cudaMemcpyAsync(out_tokens, c->d_out_tokens, (size_t) n_steps * 4, cudaMemcpyDeviceToHost, c->st));
+    SCU(cudaStreamSynchronize(c->st));
+    cudaEventElapsedTime(&c->last_ms, c->ev0, c->ev1);
+    c->launches += c->n_greedy_launches * n_steps;
+    c->n_past = pos0 + n_steps;
+    c->d_last_row = 0; c->h_last = nullptr;       // the last token's logits are on the device only
+}
+
 void stack_sync(StackCtx * c) {
     SCU(cudaSetDevice(c->m->device));
     SCU(cudaStreamSynchronize(c->st));
 }
 
 float * stack_logits_view(StackCtx * c) {
+    if (!c->h_last && c->d_last_row >= 0) {         // after a device-resident burst: fetch the row now
+        SCU(cudaSetDevice(c->m->device));
+        SCU(cudaMemcpyAsync(c->h_logits, c->d_logits + (size_t) c->d_last_row * c->m->vocab, (size_t) c->m->vocab * 4, cudaMemcpyDeviceToHost, c->st));
+        SCU(cudaStreamSynchronize(c->st));
+        c->h_last = c->h_logits;
+    }
     if (!c->h_last) throw std::runtime_error("no logits yet: the last step asked for none");
     return c->h_last;
 }

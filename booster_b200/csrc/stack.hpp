@@ -38,6 +38,7 @@ int64_t    stack_ctx_launches(const StackCtx * c);
 // are computed; logits_out (host, [n_rows][n_vocab]) may be nullptr — the last row then stays available through
 // stack_logits_view / stack_argmax. One token steps replay a captured CUDA graph.
 void    stack_decode(StackCtx * c, const int32_t * tokens, int n, int pos0, const int32_t * rows, int n_rows, float * logits_out);
+void    stack_generate_greedy(StackCtx * c, int32_t first_token, int pos0, int n_steps, int32_t * out_tokens);
 void    stack_sync(StackCtx * c);
 float * stack_logits_view(StackCtx * c);             // pinned host copy of the last computed row of logits
 int32_t stack_argmax(StackCtx * c);                  // arg-max of that row, computed on the device

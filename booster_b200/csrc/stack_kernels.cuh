@@ -938,5 +938,29 @@ __global__ void __launch_bounds__(1024) k_argmax_row(const float * __restrict__ 
     }
 }
 
+// the device-resident greedy loop's last kernel: arg-max of the token's logits becomes the next step's token at the next
+// position (header in device memory), and is appended to the list the host reads after the burst
+__global__ void __launch_bounds__(1024) k_argmax_advance(const float * __restrict__ x, int n, StepState * st, int32_t * token_slot,
+                                                         int32_t * __restrict__ out, int32_t * counter) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    float best = -INFINITY; int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = x[i]; if (v > best || (v == best && i < idx)) { best = v; idx = i; } }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int) (blockDim.x >> 5); w++) if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        if (idx == 0x7fffffff) idx = 0;
+        out[*counter] = idx;
+        *counter += 1;
+        *token_slot = idx;
+        st->pos0 += 1;
+    }
+}
+
 }  // namespace stk
 }  // namespace b200

@@ -290,6 +290,9 @@ def test_greedy_generation_through_the_bridge(tmp_path, monkeypatch):
     first = int(np.argmax(p.ctx.decode(prompt, 0)))
     dev = p.ctx.generate_greedy(first, len(prompt), n_gen - 1).tolist()
     assert [first] + dev == ids
+    # the burst left cache, state and position where a host-driven step continues them
+    after = p.ctx.decode([ids[-1]], len(prompt) + n_gen - 1)
+    assert err(after[None], lg[None]) < TOL32
     assert p.ctx.L.b200_kernel_launches(p.ctx.h) > 0
     p.close()
 
