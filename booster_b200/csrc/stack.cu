@@ -421,14 +421,29 @@ void mixer_mingru(StackCtx * c, const LayerSpec & L, int T) {
 }
 
 // launch shape of the latent attention for a pass of T tokens: queries per block, key slices, shared memory
-struct AttnPlan { int TQ, HQ, nsplit, smax; size_t smem; };
+struct AttnPlan { int TQ, HQ, nsplit, smax; size_t smem; bool staged; };
 AttnPlan plan_attention(const LayerSpec & L, int n_ctx, int T, int sm_count) {
     AttnPlan p;
     p.TQ = std::min(T, 4);
-    p.HQ = std::min(L.H, std::max(1, LAT_NQ_MAX / p.TQ));
-    if (T < 8) p.HQ = std::min(p.HQ, 4);
     const int W = L.rank + L.R;
     const int keys = L.window > 0 ? std::min(L.window + p.TQ - 1, n_ctx) : n_ctx;     // the most keys a tile can see
+    {   // staged: a block takes as many heads as it may (every cached row is fetched once per token tile) and a slice of >= 8 keys that fits shared memory
+        p.staged = true;
+        p.HQ = std::min(L.H, std::max(1, LAT_NQ_MAX / p.TQ));
+        const int blocks = ((T + p.TQ - 1) / p.TQ) * ((L.H + p.HQ - 1) / p.HQ);
+        const int WP = W % 4 == 0 ? W + 4 : (W | 1);
+        p.nsplit = std::max(1, std::min({ 2 * sm_count / blocks, (keys + 7) / 8, 64 }));
+        for (;;) {
+            p.smax = (keys + p.nsplit - 1) / p.nsplit;
+            p.smem = ((size_t) p.TQ * p.HQ * (W + p.smax + 1) + (size_t) p.smax * WP + 8) * 4;
+            if (p.smem <= 160 * 1024 || p.nsplit >= 64) break;
+            p.nsplit = std::min(64, p.nsplit * 2);
+        }
+        if (p.smem <= 160 * 1024) return p;
+    }
+    p.staged = false;                     // long unmasked contexts: the slices stay in global memory
+    p.HQ = std::min(L.H, std::max(1, LAT_NQ_MAX / p.TQ));
+    if (T < 8) p.HQ = std::min(p.HQ, 4);
     const int blocks = ((T + p.TQ - 1) / p.TQ) * ((L.H + p.HQ - 1) / p.HQ);
     p.nsplit = 1;
     if (blocks < sm_count) p.nsplit = std::max(1, std::min({ 2 * sm_count / blocks, (keys + 31) / 32, 64 }));
@@ -436,7 +451,7 @@ AttnPlan plan_attention(const LayerSpec & L, int n_ctx, int T, int sm_count) {
         p.smax = (keys + p.nsplit - 1) / p.nsplit;
         p.smem = ((size_t) p.TQ * p.HQ * (W + p.smax + 1) + 8) * 4;
         if (p.smem <= 200 * 1024 || p.nsplit >= 64) break;
-        p.nsplit *= 2;                    // long unmasked contexts: slice the keys until the scores of a block fit
+        p.nsplit *= 2;                    // slice the keys until the scores of a block fit
     }
     while (p.smem > 200 * 1024 && p.HQ > 1) { p.HQ = (p.HQ + 1) / 2; p.smem = ((size_t) p.TQ * p.HQ * (W + p.smax + 1) + 8) * 4; }
     return p;
@@ -489,8 +504,11 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
     }
     const AttnPlan ap = plan_attention(L, c->n_ctx, T, c->sm_count);
     const LatAttnArgs aa{c->QK, cache, L.sink, &c->d_step->st, c->OL, c->att_part, c->att_ml, T, H, rank, R, L.window, L.scale, ap.TQ, ap.HQ, ap.nsplit, ap.smax};
-    k_latent_attn<<<dim3((unsigned) ((T + ap.TQ - 1) / ap.TQ), (unsigned) ((H + ap.HQ - 1) / ap.HQ), (unsigned) ap.nsplit), 256, ap.smem, c->st>>>(aa);
-    if (ap.nsplit > 1) { k_latent_combine<<<dim3((unsigned) T, (unsigned) H), 128, 0, c->st>>>(aa); c->launches++; }
+    const dim3 grid((unsigned) ((T + ap.TQ - 1) / ap.TQ), (unsigned) ((H + ap.HQ - 1) / ap.HQ), (unsigned) ap.nsplit);
+    if (!ap.staged) k_latent_attn<<<grid, 256, ap.smem, c->st>>>(aa);
+    else if (W % 4 == 0) k_latent_attn_staged<true><<<grid, 256, ap.smem, c->st>>>(aa);
+    else k_latent_attn_staged<false><<<grid, 256, ap.smem, c->st>>>(aa);
+    if (ap.nsplit > 1) { k_latent_combine<<<dim3((unsigned) T, (unsigned) H, (unsigned) ((rank + 63) / 64)), 256, 0, c->st>>>(aa); c->launches++; }
     // values, one product per head: A[t][h] = W_uv,h (sum_j w_j c_j)
     linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
     linear(c, c->A, H * V, L.o, c->Y, E, T);
@@ -688,7 +706,7 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
                 const size_t all = (cap_t / ATT_TQ) * one;
                 c->att_scores_floats = std::max(c->att_scores_floats, std::min(all, std::max(one, ATT_SCORE_BYTES / 4)));
             }
-            for (int T = 1; T <= c->cap; T++) {           // every pass size has its plan: the buffers cover the largest
+            for (int T = 1; T <= std::min(c->cap, 7); T++) {      // the pass sizes that take the decode kernels: the buffers cover the largest plan
                 const AttnPlan ap = plan_attention(L, n_ctx, T, c->sm_count);
                 smem = std::max(smem, ap.smem);
                 if (ap.nsplit > 1) { part = std::max(part, (size_t) T * L.H * ap.nsplit * L.rank); ml = std::max(ml, (size_t) T * L.H * ap.nsplit * 2); }
@@ -700,7 +718,12 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         if (c->att_scores_floats) fl(&c->att_scores, c->att_scores_floats);
         {   // the opt-in limit is a property of the kernel, not of a context: it only ever grows
             static size_t attr = 48 * 1024;
-            if (smem > attr) { SCU(cudaFuncSetAttribute(k_latent_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)); attr = smem; }
+            if (smem > attr) {
+                SCU(cudaFuncSetAttribute(k_latent_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+                SCU(cudaFuncSetAttribute(k_latent_attn_staged<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+                SCU(cudaFuncSetAttribute(k_latent_attn_staged<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+                attr = smem;
+            }
         }
         SCU(cudaMalloc(&c->d_step, sizeof(StepDev)));
         SCU(cudaMemsetAsync(c->d_step, 0, sizeof(StepDev), c->st));

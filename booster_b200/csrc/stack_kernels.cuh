@@ -15,6 +15,7 @@
 namespace b200 {
 namespace stk {
 
+
 __device__ __forceinline__ float wf(const float * p, size_t i) { return p[i]; }
 __device__ __forceinline__ float wf(const __nv_bfloat16 * p, size_t i) { return __bfloat162float(p[i]); }
 __device__ __forceinline__ float warp_sum(float v) {
@@ -763,8 +764,135 @@ __global__ void __launch_bounds__(256) k_latent_attn(const LatAttnArgs a) {
         }
     }
 }
+// The same step for decode when a block's key slice fits shared memory: asynchronous copies bring the slice's cached rows in
+// all at once (no chain of dependent loads), and scores and weighted sum read them from there. A thread owns one
+// (query, key) score; the weighted sum keeps k_latent_attn's ownership (LAT_RPT latent entries, all queries). VEC: rows are
+// whole 16-byte chunks (rank + R a multiple of 4); otherwise 4-byte copies. Rows are padded so that the keys of a warp fall
+// into different banks. Same results layout (OL, or part / ml for k_latent_combine) as k_latent_attn.
+template <bool VEC>
+__global__ void __launch_bounds__(256) k_latent_attn_staged(const LatAttnArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int W = a.rank + a.R, WP = VEC ? W + 4 : (W | 1), NQ = a.TQ * a.HQ;
+    const int t0 = blockIdx.x * a.TQ, h0 = blockIdx.y * a.HQ, z = blockIdx.z;
+    const int nt = min(a.TQ, a.T - t0);
+    const int p_first = a.st->pos0 + t0, p_last = p_first + nt - 1;
+    const int jlo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    const int nkeys = p_last - jlo + 1;
+    const int chunk = (nkeys + a.nsplit - 1) / a.nsplit;
+    const int jb = jlo + z * chunk, je = min(jb + chunk, p_last + 1), nk = max(je - jb, 0);      // this block's keys [jb, je)
+    float * q = sm;                                   // [NQ][W]
+    float * keys = q + (size_t) NQ * W;               // [smax][WP]
+    float * s = keys + (size_t) a.smax * WP;          // [NQ][smax]
+    float * inv = s + (size_t) NQ * a.smax;           // [NQ]
+    {
+        const float * src = a.cache + (size_t) jb * W;
+        const uint32_t dst = (uint32_t) __cvta_generic_to_shared(keys);
+        if (VEC) {
+            const int w4 = W >> 2;
+            for (int i = tid; i < nk * w4; i += 256) {
+                const int j = i / w4, e = (i - j * w4) << 2;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + (uint32_t) (j * WP + e) * 4u), "l"(src + (size_t) j * W + e) : "memory");
+            }
+        } else {
+            for (int i = tid; i < nk * W; i += 256) {
+                const int j = i / W, e = i - j * W;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst + (uint32_t) (j * WP + e) * 4u), "l"(src + (size_t) j * W + e) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int i = tid; i < NQ * W; i += 256) {
+        const int qi = i / W, e = i % W, tq = qi / a.HQ, h = h0 + qi % a.HQ;
+        q[i] = (tq < nt && h < a.H) ? a.QK[((size_t) (t0 + tq) * a.H + h) * W + e] : 0.f;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    // scores: a thread per (query, key); neighbouring threads take neighbouring keys of one query
+    for (int pr = tid; pr < NQ * nk; pr += 256) {
+        const int qi = pr / nk, j = pr - qi * nk;
+        const float * qv = q + (size_t) qi * W, * kv = keys + (size_t) j * WP;
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+        if (VEC) {
+            for (int e = 0; e < W; e += 4) {
+                const float4 x = *reinterpret_cast<const float4 *>(qv + e), y = *reinterpret_cast<const float4 *>(kv + e);
+                acc0 = fmaf(x.x, y.x, acc0); acc1 = fmaf(x.y, y.y, acc1); acc2 = fmaf(x.z, y.z, acc2); acc3 = fmaf(x.w, y.w, acc3);
+            }
+        } else {
+            for (int e = 0; e < W; e++) acc0 = fmaf(qv[e], kv[e], acc0);
+        }
+        const float v = ((acc0 + acc1) + (acc2 + acc3)) * a.scale;
+        const int tq = qi / a.HQ, p = p_first + tq, key = jb + j;
+        const bool ok = tq < nt && h0 + qi % a.HQ < a.H && key <= p && (a.window <= 0 || p - key < a.window);
+        s[(size_t) qi * a.smax + j] = ok ? v : -INFINITY;
+    }
+    __syncthreads();
+    // soft-max per query: one warp per query
+    for (int qi = warp; qi < NQ; qi += 8) {
+        float * row = s + (size_t) qi * a.smax;
+        const int tq = qi / a.HQ, h = h0 + qi % a.HQ;
+        const bool live = tq < nt && h < a.H;
+        float mx = -INFINITY;
+        for (int j = lane; j < nk; j += 32) mx = fmaxf(mx, row[j]);
+        mx = warp_max(mx);
+        const float snk = (a.sink && live) ? a.sink[h] : -INFINITY;
+        const float m = a.nsplit == 1 ? fmaxf(mx, snk) : mx;
+        float sum = 0.f;
+        for (int j = lane; j < nk; j += 32) { const float e = m == -INFINITY ? 0.f : expf(row[j] - m); row[j] = e; sum += e; }
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            if (a.nsplit == 1) {
+                const float den = sum + (snk == -INFINITY ? 0.f : expf(snk - m));
+                inv[qi] = den > 0.f ? 1.0f / den : 0.f;
+            } else {
+                inv[qi] = 1.0f;
+                if (live) {
+                    float * o = a.ml + (((size_t) (t0 + tq) * a.H + h) * a.nsplit + z) * 2;
+                    o[0] = m; o[1] = sum;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // weighted sum of the latents: a thread owns LAT_RPT entries of the latent for all NQ queries
+    for (int rb = 0; rb < a.rank; rb += 256 * LAT_RPT) {
+        float acc[LAT_NQ_MAX][LAT_RPT];
+#pragma unroll
+        for (int qi = 0; qi < LAT_NQ_MAX; qi++)
+#pragma unroll
+            for (int k = 0; k < LAT_RPT; k++) acc[qi][k] = 0.f;
+        for (int j = 0; j < nk; j++) {
+            const float * c = keys + (size_t) j * WP + rb + tid;
+            float cv[LAT_RPT];
+#pragma unroll
+            for (int k = 0; k < LAT_RPT; k++) cv[k] = rb + tid + 256 * k < a.rank ? c[256 * k] : 0.f;
+#pragma unroll
+            for (int qi = 0; qi < LAT_NQ_MAX; qi++) {
+                if (qi < NQ) {
+                    const float w = s[(size_t) qi * a.smax + j];
+#pragma unroll
+                    for (int k = 0; k < LAT_RPT; k++) acc[qi][k] = fmaf(w, cv[k], acc[qi][k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int qi = 0; qi < LAT_NQ_MAX; qi++) {
+            if (qi >= NQ) continue;
+            const int tq = qi / a.HQ, h = h0 + qi % a.HQ;
+            if (tq >= nt || h >= a.H) continue;
+            const size_t th = (size_t) (t0 + tq) * a.H + h;
+            float * o = a.nsplit == 1 ? a.OL + th * a.rank : a.part + (th * a.nsplit + z) * a.rank;
+#pragma unroll
+            for (int k = 0; k < LAT_RPT; k++) {
+                const int r = rb + tid + 256 * k;
+                if (r < a.rank) o[r] = acc[qi][k] * inv[qi];
+            }
+        }
+    }
+}
+
 // merge of the key slices of one (token, head): weights exp(m_z - M) with M the largest maximum (the sink included)
-__global__ void k_latent_combine(const LatAttnArgs a) {
+__global__ void __launch_bounds__(256) k_latent_combine(const LatAttnArgs a) {       // grid (T, H, ceil(rank / 64)): 64 latent entries x 4 groups of slices
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t th = (size_t) t * a.H + h;
     const float * ml = a.ml + th * a.nsplit * 2;
@@ -775,14 +903,18 @@ __global__ void k_latent_combine(const LatAttnArgs a) {
     for (int z = 0; z < a.nsplit; z++) if (ml[2 * z] != -INFINITY) den += ml[2 * z + 1] * expf(ml[2 * z] - M);
     const float inv = den > 0.f ? 1.0f / den : 0.f;
     __shared__ float wz[64];            // nsplit <= 64
+    __shared__ float red[4][64];
     if (threadIdx.x < a.nsplit) wz[threadIdx.x] = ml[2 * threadIdx.x] != -INFINITY ? expf(ml[2 * threadIdx.x] - M) * inv : 0.f;
     __syncthreads();
-    for (int r = threadIdx.x; r < a.rank; r += blockDim.x) {
-        float acc = 0.f;
+    const int r = blockIdx.z * 64 + (threadIdx.x & 63), g = threadIdx.x >> 6;
+    float acc = 0.f;
+    if (r < a.rank) {
 #pragma unroll 8
-        for (int z = 0; z < a.nsplit; z++) acc = fmaf(a.part[(th * a.nsplit + z) * a.rank + r], wz[z], acc);     // empty slices wrote zeros
-        a.OL[th * a.rank + r] = acc;
+        for (int z = g; z < a.nsplit; z += 4) acc = fmaf(a.part[(th * a.nsplit + z) * a.rank + r], wz[z], acc);     // empty slices wrote zeros
     }
+    red[g][threadIdx.x & 63] = acc;
+    __syncthreads();
+    if (g == 0 && r < a.rank) a.OL[th * a.rank + r] = (red[0][threadIdx.x] + red[1][threadIdx.x]) + (red[2][threadIdx.x] + red[3][threadIdx.x]);
 }
 
 // Prompt portions compute the same attention as two float32 products around a row soft-max (all on the CUDA cores: scores and

@@ -239,6 +239,58 @@ def test_other_sizes(tmp_path, width, groups, vocab):
     p.close()
 
 
+def random_config(rng):
+    """a random arrangement of the three mixers with random sizes: nothing may rest on one model's values"""
+    pick = lambda values: int(rng.choice(values))
+    groups = pick([1, 2, 3, 4, 5, 8])
+    layers = []
+    for _ in range(pick([2, 3, 4, 5])):
+        mlp = ff(pick([24, 64, 100, 136]), float(rng.choice([0.5, 1.0, 7.0]))) if rng.random() < 0.5 else None
+        kind = pick([0, 1, 2])
+        if kind == 0:
+            layers.append(mingru(pick([8, 24, 56, 130]), mlp))
+        elif kind == 1:
+            rot_dim = pick([2, 4, 8, 16, 32])
+            L = latent(heads=pick([1, 2, 3, 5, 6, 12]), dim=pick([4, 8, 24, 64]), rot_dim=rot_dim, vdim=pick([4, 16, 40, 64]), kv_rank=pick([8, 24, 64, 96, 192]),
+                       window=pick([0, 1, 3, 17, 64, 100, 300]), scaling=bool(rng.random() < 0.7), dims=rot_dim if rng.random() < 0.6 else pick([d for d in (2, 4, 8, 16) if d <= rot_dim]),
+                       mlp=mlp, scale=float(rng.choice([0.1, 0.2, 0.35])))
+            if "scaling" in L["mixer"]["rot"]:
+                L["mixer"]["rot"]["scaling"] = {"factor": float(rng.choice([2.0, 8.0, 40.0])), "fast": float(rng.choice([32.0, 16.0])), "slow": float(rng.choice([1.0, 2.0])),
+                                                "original": pick([16, 64, 4096])}
+                L["mixer"]["rot"]["base"] = float(rng.choice([10000.0, 500000.0]))
+            layers.append(L)
+        else:
+            kv = pick([1, 2, 3])
+            layers.append(delta(heads=kv * pick([1, 2, 4]), kv_heads=kv, dim=pick([4, 16, 32, 128]), vdim=pick([4, 8, 48, 128]), conv=pick([1, 2, 3, 5]), mlp=mlp))
+    return config(layers, width=groups * pick([8, 12, 24, 40, 72]), vocab=pick([37, 100, 257, 513]), groups=groups, eps=float(rng.choice([1e-6, 1e-5])))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(tmp_path, seed):
+    rng = np.random.default_rng(500 + seed)
+    cfg = random_config(rng)
+    n = int(rng.choice([70, 150, 330]))
+    p = Pair(tmp_path, cfg, seed=seed, n_ctx=n + 4)
+    toks = p.tokens(n, seed=seed)
+    want = p.expected(toks)
+    assert err(p.run(toks), want) < 2 * TOL32, cfg
+    assert err(p.run(toks, [n - 20] + [1] * 20), want) < 2 * TOL32, cfg
+    assert err(p.run(toks, [2, 67, 3, 129, 1, 5]), want) < 2 * TOL32, cfg
+    p.close()
+
+
+def test_a_step_longer_than_one_pass(tmp_path):
+    """a 700-token step runs as two passes of the layers: the window, the convolution's inputs and the recurrent state cross the pass's edge"""
+    layers = [latent(heads=3, dim=8, rot_dim=4, vdim=8, kv_rank=16, window=40), delta(heads=2, kv_heads=1, dim=8, vdim=8, conv=4), mingru(24, ff(40)),
+              latent(heads=2, dim=8, rot_dim=8, vdim=4, kv_rank=24, window=0)]
+    p = Pair(tmp_path, config(layers), n_ctx=704)
+    toks = p.tokens(700, seed=5)
+    want = p.expected(toks)
+    assert err(p.run(toks), want) < 2 * TOL32
+    assert err(p.run(toks, [509, 2, 3, 186]), want) < 2 * TOL32
+    p.close()
+
+
 def row_errs(got, want):
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     d = got - want
