@@ -785,26 +785,34 @@ __global__ void __launch_bounds__(256) k_latent_attn_staged(const LatAttnArgs a)
     float * keys = q + (size_t) NQ * W;               // [smax][WP]
     float * s = keys + (size_t) a.smax * WP;          // [NQ][smax]
     float * inv = s + (size_t) NQ * a.smax;           // [NQ]
-    {
+    {   // the slice's cached rows and the block's queries: every copy is issued before any is waited for
         const float * src = a.cache + (size_t) jb * W;
-        const uint32_t dst = (uint32_t) __cvta_generic_to_shared(keys);
+        const uint32_t dst = (uint32_t) __cvta_generic_to_shared(keys), qdst = (uint32_t) __cvta_generic_to_shared(q);
         if (VEC) {
             const int w4 = W >> 2;
             for (int i = tid; i < nk * w4; i += 256) {
                 const int j = i / w4, e = (i - j * w4) << 2;
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst + (uint32_t) (j * WP + e) * 4u), "l"(src + (size_t) j * W + e) : "memory");
             }
+            for (int i = tid; i < NQ * w4; i += 256) {
+                const int qi = i / w4, e = (i - qi * w4) << 2, tq = qi / a.HQ, h = h0 + qi % a.HQ;
+                if (tq < nt && h < a.H)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(qdst + (uint32_t) (qi * W + e) * 4u), "l"(a.QK + ((size_t) (t0 + tq) * a.H + h) * W + e) : "memory");
+                else *reinterpret_cast<float4 *>(q + (size_t) qi * W + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         } else {
             for (int i = tid; i < nk * W; i += 256) {
                 const int j = i / W, e = i - j * W;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(dst + (uint32_t) (j * WP + e) * 4u), "l"(src + (size_t) j * W + e) : "memory");
             }
+            for (int i = tid; i < NQ * W; i += 256) {
+                const int qi = i / W, e = i - qi * W, tq = qi / a.HQ, h = h0 + qi % a.HQ;
+                if (tq < nt && h < a.H)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(qdst + (uint32_t) (qi * W + e) * 4u), "l"(a.QK + ((size_t) (t0 + tq) * a.H + h) * W + e) : "memory");
+                else q[(size_t) qi * W + e] = 0.f;
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    for (int i = tid; i < NQ * W; i += 256) {
-        const int qi = i / W, e = i % W, tq = qi / a.HQ, h = h0 + qi % a.HQ;
-        q[i] = (tq < nt && h < a.H) ? a.QK[((size_t) (t0 + tq) * a.H + h) * W + e] : 0.f;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
