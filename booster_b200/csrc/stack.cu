@@ -430,9 +430,13 @@ AttnPlan plan_attention(const LayerSpec & L, int n_ctx, int T, int sm_count) {
     {   // staged: a block takes as many heads as it may (every cached row is fetched once per token tile) and a slice of >= 8 keys that fits shared memory
         p.staged = true;
         p.HQ = std::min(L.H, std::max(1, LAT_NQ_MAX / p.TQ));
-        const int blocks = ((T + p.TQ - 1) / p.TQ) * ((L.H + p.HQ - 1) / p.HQ);
+        int blocks = ((T + p.TQ - 1) / p.TQ) * ((L.H + p.HQ - 1) / p.HQ);
         const int WP = W % 4 == 0 ? W + 4 : (W | 1);
         p.nsplit = std::max(1, std::min({ 2 * sm_count / blocks, (keys + 7) / 8, 64 }));
+        while (blocks * p.nsplit < sm_count && p.HQ > 4) {      // SMs left idle: fewer heads per block (the rows come from L2 again)
+            p.HQ = (p.HQ + 1) / 2;
+            blocks = ((T + p.TQ - 1) / p.TQ) * ((L.H + p.HQ - 1) / p.HQ);
+        }
         for (;;) {
             p.smax = (keys + p.nsplit - 1) / p.nsplit;
             p.smem = ((size_t) p.TQ * p.HQ * (W + p.smax + 1) + (size_t) p.smax * WP + 8) * 4;

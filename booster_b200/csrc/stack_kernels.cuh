@@ -765,7 +765,7 @@ __global__ void __launch_bounds__(256) k_latent_attn(const LatAttnArgs a) {
     }
 }
 // The same step for decode when a block's key slice fits shared memory: asynchronous copies bring the slice's cached rows in
-// all at once (no chain of dependent loads), and scores and weighted sum read them from there. A thread owns one
+// all at once (no chain of dependent loads), and scores and weighted sum read them from there. One to eight lanes own a
 // (query, key) score; the weighted sum keeps k_latent_attn's ownership (LAT_RPT latent entries, all queries). VEC: rows are
 // whole 16-byte chunks (rank + R a multiple of 4); otherwise 4-byte copies. Rows are padded so that the keys of a warp fall
 // into different banks. Same results layout (OL, or part / ml for k_latent_combine) as k_latent_attn.
@@ -816,23 +816,31 @@ __global__ void __launch_bounds__(256) k_latent_attn_staged(const LatAttnArgs a)
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    // scores: a thread per (query, key); neighbouring threads take neighbouring keys of one query
-    for (int pr = tid; pr < NQ * nk; pr += 256) {
-        const int qi = pr / nk, j = pr - qi * nk;
+    // scores: `spl` neighbouring lanes share one (query, key) dot product when there are fewer scores than threads
+    const int npairs = NQ * nk;
+    int spl = 1;
+    while (spl < 8 && npairs * spl * 2 <= 256) spl *= 2;
+    for (int base = 0; base < npairs; base += 256 / spl) {
+        const int pr = base + tid / spl, part = tid & (spl - 1);
+        const bool live = pr < npairs;
+        const int qi = live ? pr / nk : 0, j = live ? pr - qi * nk : 0;
         const float * qv = q + (size_t) qi * W, * kv = keys + (size_t) j * WP;
+        const int lim = live ? W : 0;
         float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
         if (VEC) {
-            for (int e = 0; e < W; e += 4) {
+            for (int e = part * 4; e < lim; e += 4 * spl) {
                 const float4 x = *reinterpret_cast<const float4 *>(qv + e), y = *reinterpret_cast<const float4 *>(kv + e);
                 acc0 = fmaf(x.x, y.x, acc0); acc1 = fmaf(x.y, y.y, acc1); acc2 = fmaf(x.z, y.z, acc2); acc3 = fmaf(x.w, y.w, acc3);
             }
         } else {
-            for (int e = 0; e < W; e++) acc0 = fmaf(qv[e], kv[e], acc0);
+            for (int e = part; e < lim; e += spl) acc0 = fmaf(qv[e], kv[e], acc0);
         }
-        const float v = ((acc0 + acc1) + (acc2 + acc3)) * a.scale;
+        float v = (acc0 + acc1) + (acc2 + acc3);
+        for (int o = 1; o < spl; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        v *= a.scale;
         const int tq = qi / a.HQ, p = p_first + tq, key = jb + j;
         const bool ok = tq < nt && h0 + qi % a.HQ < a.H && key <= p && (a.window <= 0 || p - key < a.window);
-        s[(size_t) qi * a.smax + j] = ok ? v : -INFINITY;
+        if (live && part == 0) s[(size_t) qi * a.smax + j] = ok ? v : -INFINITY;
     }
     __syncthreads();
     // soft-max per query: one warp per query
