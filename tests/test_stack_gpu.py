@@ -279,6 +279,20 @@ def test_random_configurations(tmp_path, seed):
     p.close()
 
 
+def test_large_heads_and_ranks(tmp_path):
+    """more heads than one attention block takes, a latent wider than one sweep of the weighted sum, a row that is no whole number
+    of 16-byte chunks, and a delta-rule key size that takes the widest recurrence kernel"""
+    layers = [latent(heads=20, dim=16, rot_dim=32, vdim=24, kv_rank=640, window=70), latent(heads=7, dim=20, rot_dim=6, vdim=10, kv_rank=37, window=129, dims=6),
+              delta(heads=2, kv_heads=1, dim=192, vdim=80, conv=2)]
+    p = Pair(tmp_path, config(layers, width=128, vocab=90, groups=2), seed=2, n_ctx=208)
+    toks = p.tokens(200, seed=8)
+    want = p.expected(toks)
+    assert err(p.run(toks), want) < TOL32
+    assert err(p.run(toks, [170] + [1] * 30), want) < TOL32
+    assert err(p.run(toks, [2, 67, 3]), want) < TOL32
+    p.close()
+
+
 def test_a_step_longer_than_one_pass(tmp_path):
     """a 700-token step runs as two passes of the layers: the window, the convolution's inputs and the recurrent state cross the pass's edge"""
     layers = [latent(heads=3, dim=8, rot_dim=4, vdim=8, kv_rank=16, window=40), delta(heads=2, kv_heads=1, dim=8, vdim=8, conv=4), mingru(24, ff(40)),
