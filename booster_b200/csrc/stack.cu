@@ -3,8 +3,14 @@
 // the registry of designs and mixers. Kernels: stack_kernels.cuh. C-ABI dispatch: engine.cu.
 //
 // A design is a name in config.json ("architecture") mapped to a builder that turns the configuration into a list of
-// LayerSpec; a mixer is a name ("type") mapped to a loader of its tensors and a forward routine. Matulorn is the first
-// design of the family; its three mixers are registered below and can be combined in any order and size.
+// LayerSpec; a mixer is a name ("type") mapped to a loader of its tensors and a forward routine. Two designs are registered:
+//   Matulorn   sequential sub-layers with grouped norms before and after each; mixers minGRU | latent attention (rotated
+//              part, window, sink) | gated delta rule; clamped gated feed-forward
+//   Dopilorn   both sub-layers read the same residual (x += mixer(n1 x) + ff(n2 x)) behind a causal convolution of their
+//              inputs; mixers latent attention (query latent, head gates) | generalized delta rule | differential
+//              sliding-window attention; polynomial feed-forward; a span of layers run several times with the same weights
+//              (each pass with a state of its own); soft-capped logits
+// A model is executed as a list of layer RUNS: (layer, state slot), one per layer unless the design repeats some.
 #include "stack.hpp"
 #include "safetensors.hpp"
 #include "stack_kernels.cuh"
@@ -25,7 +31,9 @@ using namespace stk;
 
 namespace {
 
-enum MixerKind { MIX_MINGRU = 0, MIX_LATENT, MIX_DELTA };
+enum MixerKind { MIX_MINGRU = 0, MIX_LATENT, MIX_DELTA, MIX_GDELTA, MIX_DIFFATTN };
+enum BlockKind { BLOCK_SEQUENTIAL = 0, BLOCK_PARALLEL };
+enum FfKind { FF_GLU = 0, FF_POLY };
 constexpr int CHUNK_MAX = 512;          // tokens per pass of a prompt portion (longer steps run as several passes)
 constexpr float GLU_ALPHA = 1.702f;     // the feed-forward's sigmoid slope: fixed by the design
 
@@ -50,17 +58,36 @@ struct LayerSpec {
     int rope_dims = 0;
     float rope_mag = 1.f;
     DMat qdkv, ukT, uv;                  // q | down-projection stacked; per head: W_uk transposed [rank][D], W_uv [V][rank]
+    int q_rank = 0;                      // > 0: queries pass a latent of their own; qdkv is then [ query latent | down-projection | head gates ]
+    DMat uq;                             // query latent -> H x D
+    float * qnorm = nullptr;
+    bool head_gate = false;
     // gated delta rule
     int KH = 0, taps = 0;
     DMat proj;                           // q | k | v | beta | decay | gate stacked
     float * wconv = nullptr, * A_log = nullptr, * dt_bias = nullptr, * dnorm = nullptr;
+    // generalized delta rule: proj = r | k | v | gate | removal | decay latent; w2 maps the decay latent to H x D (bias: w0)
+    int lora = 0;
+    DMat w2;
+    // differential attention: proj = q | k | v with biases; G = KH; lambda is one number per layer
+    float lambda = 0.f, diff = 0.f;
     // feed-forward
-    int ff = 0;
+    int ff = 0, ff_kind = FF_GLU;
     float limit = 0.f;
-    DMat gateup, down;
-    // state layout (float offsets)
-    size_t off_rec = 0, n_rec = 0;       // recurrent slab: minGRU state | delta S + conv history
-    size_t cache_row = 0;                // latent attention: floats per cached position
+    DMat gateup, down;                   // FF_POLY: gateup is the plain up-projection
+    float * act = nullptr;               // FF_POLY: the four coefficients
+    // parallel blocks: weights of the causal convolution in front of each sub-layer, [2][E][taps]
+    float * canon = nullptr;
+    // state a sequence keeps for one run of this layer
+    size_t n_rec = 0;                    // recurrent slab (floats): minGRU state | delta S + conv history | ... ; then the input convolutions' history
+    size_t cache_row = 0;                // attention: floats per cached position (0: no cache)
+    int64_t bytes = 0;                   // weights one token reads in this layer
+};
+
+struct RunSpec {                         // one execution of a layer within a step
+    int layer = 0;
+    int pass = -1;                       // >= 0: this run opens pass `pass` of the repeated span (x <- W_in [x; x0] + step[pass] first)
+    size_t off_rec = 0;
     int cache_index = -1;
 };
 
@@ -71,7 +98,13 @@ struct StackModel {
     std::string design;
     int vocab = 0, E = 0, groups = 1;
     float eps = 1e-6f;
+    int block = BLOCK_SEQUENTIAL;
+    int canon_taps = 0;                   // parallel blocks: taps of the input convolutions (0: none)
+    float softcap = 0.f;                  // > 0: logits <- cap tanh(logits / cap)
+    DMat loop_in;                         // repeated span: [E][2 E]
+    float * loop_step = nullptr;          // [times][E]
     std::vector<LayerSpec> layers;
+    std::vector<RunSpec> runs;
     void * embed = nullptr;
     float * final_norm = nullptr;
     DMat head;
@@ -93,9 +126,12 @@ struct StackCtx {
     StackModel * m = nullptr;
     int n_ctx = 0, n_past = 0, cap = 0;
     cudaStream_t st = nullptr;
+    float * Y2 = nullptr, * U = nullptr, * XC = nullptr;     // parallel blocks: the feed-forward's output, the convolved inputs [2][cap][E], [x; x0] rows
+    const float * in = nullptr;           // what the mixer being enqueued reads ([T][E]) ...
+    float * out = nullptr;                // ... and writes
     float * X = nullptr, * Hn = nullptr, * Y = nullptr, * P = nullptr, * A = nullptr, * QK = nullptr, * OL = nullptr, * CV = nullptr, * BG = nullptr, * O = nullptr;
     float * rec = nullptr;                // recurrent slab
-    std::vector<float *> caches;          // per latent-attention layer: [n_ctx][rank + R]
+    std::vector<float *> caches;          // per run of an attention layer: [n_ctx][cache_row]
     StepDev * d_step = nullptr, * h_step = nullptr;
     float * d_logits = nullptr, * h_logits = nullptr;
     int64_t logit_rows_cap = 0;
@@ -186,14 +222,30 @@ void load_mingru(StackModel & m, LayerSpec & L, const Json & mx, const safetenso
 
 void load_latent(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
     const int E = m.E;
-    const int H = L.H = need_int(mx, "heads"), D = L.D = need_int(mx, "dim"), R = L.R = need_int(mx, "rot_dim", 0);
+    const int H = L.H = need_int(mx, "heads"), D = L.D = need_int(mx, "dim"), R = L.R = (int) mx.integer("rot_dim", 0);
     const int V = L.V = need_int(mx, "vdim"), rank = L.rank = need_int(mx, "kv_rank");
+    if (R < 0) throw std::runtime_error("config: rot_dim must not be negative");
     L.scale = (float) mx.number("scale");
     L.window = mx.has("mask") ? (int) mx.at("mask").integer("size", 0) : 0;       // 0: every earlier position
     if (L.window < 0) throw std::runtime_error("config: mask.size must not be negative");
-    std::vector<float> W = sf.read_f32(p + "q", {H * (D + R), E});
-    append(W, sf.read_f32(p + "dkv", {rank + R, E}));
-    L.qdkv = up_mat(m, W, H * (D + R) + rank + R, E, nullptr);
+    const int qr = L.q_rank = (int) mx.integer("q_rank", 0);
+    if (qr < 0) throw std::runtime_error("config: q_rank must not be negative");
+    L.head_gate = sf.find(p + "g") != nullptr;
+    if (qr > 0) {
+        // queries through a latent: [ W_dq | W_dkv | W_g ] in one product, then norm and W_uq
+        if (R) throw std::runtime_error("latent attention: a query latent with a rotated part is not implemented");
+        std::vector<float> W = sf.read_f32(p + "dq", {qr, E});
+        append(W, sf.read_f32(p + "dkv", {rank, E}));
+        if (L.head_gate) append(W, sf.read_f32(p + "g", {H, E}));
+        L.qdkv = up_mat(m, W, qr + rank + (L.head_gate ? H : 0), E, nullptr);
+        L.qnorm = up_f32(m, sf.read_f32(p + "dq.norm", {qr}));
+        L.uq = up_mat(m, sf.read_f32(p + "uq", {H * D, qr}), H * D, qr, nullptr);
+    } else {
+        std::vector<float> W = sf.read_f32(p + "q", {H * (D + R), E});
+        append(W, sf.read_f32(p + "dkv", {rank + R, E}));
+        if (L.head_gate) append(W, sf.read_f32(p + "g", {H, E}));
+        L.qdkv = up_mat(m, W, H * (D + R) + rank + R + (L.head_gate ? H : 0), E, nullptr);
+    }
     L.cnorm = up_f32(m, sf.read_f32(p + "dkv.norm", {rank}));
     // W_uk [H*D][rank] -> per head transposed [rank][D]: the unrotated score q_h . (W_uk,h c) = (W_uk,h^T q_h) . c
     const std::vector<float> uk = sf.read_f32(p + "uk", {H * D, rank});
@@ -235,8 +287,7 @@ void load_latent(StackModel & m, LayerSpec & L, const Json & mx, const safetenso
     }
     L.rope_freq = up_f32(m, freq);
     L.cache_row = (size_t) rank + R;
-    L.cache_index = m.n_caches++;
-    m.maxP = std::max(m.maxP, H * (D + R) + rank + R); m.maxA = std::max(m.maxA, H * V);
+    m.maxP = std::max(m.maxP, L.qdkv.N); m.maxA = std::max({ m.maxA, H * V, qr > 0 ? H * D : 0 });
     m.maxQK = std::max(m.maxQK, H * (rank + R)); m.maxOL = std::max(m.maxOL, H * rank);
 }
 
@@ -265,12 +316,95 @@ void load_delta(StackModel & m, LayerSpec & L, const Json & mx, const safetensor
     m.maxCV = std::max(m.maxCV, C); m.maxBG = std::max(m.maxBG, 2 * H);
 }
 
+// generalized delta rule: '<layer>.mix.{r,k,v,g,a,a.b,w1,w2,w0,norm,o}'
+void load_gdelta(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E;
+    const int H = L.H = need_int(mx, "heads"), D = L.D = need_int(mx, "dim"), V = L.V = (int) mx.integer("vdim", D);
+    if (V < 1) throw std::runtime_error("config: vdim out of range");
+    if (D > 256) throw std::runtime_error("generalized delta rule: dim above 256 is not supported by the recurrence kernel");
+    const st_tensor * w1 = sf.find(p + "w1");
+    if (!w1 || w1->shape.size() != 2) throw std::runtime_error("tensor '" + p + "w1' is missing or not a matrix");
+    const int lr = L.lora = (int) w1->shape[0];
+    std::vector<float> W = sf.read_f32(p + "r", {H * D, E}), b((size_t) 2 * H * D + 2 * H * V, 0.f);
+    append(W, sf.read_f32(p + "k", {H * D, E}));
+    append(W, sf.read_f32(p + "v", {H * V, E}));
+    append(W, sf.read_f32(p + "g", {H * V, E}));
+    append(W, sf.read_f32(p + "a", {H * D, E})); append(b, sf.read_f32(p + "a.b", {H * D}));
+    append(W, sf.read_f32(p + "w1", {lr, E}));   b.resize(b.size() + (size_t) lr, 0.f);
+    const int NP = 3 * H * D + 2 * H * V + lr;
+    L.proj = up_mat(m, W, NP, E, &b);
+    const std::vector<float> w0 = sf.read_f32(p + "w0", {H * D});
+    L.w2 = up_mat(m, sf.read_f32(p + "w2", {H * D, lr}), H * D, lr, &w0);
+    L.dnorm = up_f32(m, sf.read_f32(p + "norm", {H * V}));
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
+    L.n_rec = (size_t) H * D * V;
+    m.maxP = std::max(m.maxP, NP); m.maxA = std::max(m.maxA, H * V);
+    m.maxCV = std::max(m.maxCV, 3 * H * D); m.maxBG = std::max(m.maxBG, H * D);
+}
+
+// differential sliding-window attention: '<layer>.mix.{q,k,v}' with '.b' and '.conv', 'lq1','lk1','lq2','lk2', 'o'
+void load_diffattn(StackModel & m, LayerSpec & L, const Json & mx, const safetensors_file & sf, const std::string & p) {
+    const int E = m.E;
+    const int H = L.H = need_int(mx, "heads"), G = L.KH = (int) mx.integer("kv_heads", H), D = L.D = need_int(mx, "dim"), V = L.V = need_int(mx, "vdim");
+    if (G < 1 || H % G) throw std::runtime_error("config: attention heads must be a multiple of kv_heads");
+    if (V > 256) throw std::runtime_error("differential attention: vdim above 256 is not supported by the attention kernel");
+    if (D > 256) throw std::runtime_error("differential attention: dim above 256 is not supported by the attention kernel");
+    const int taps = L.taps = (int) mx.integer("conv", 0);              // 0: no convolution after the projections
+    if (taps < 0 || taps > 64) throw std::runtime_error("config: attention conv taps out of range");
+    L.scale = (float) mx.number("scale");
+    L.diff = (float) mx.number("diff");
+    L.window = mx.has("mask") ? (int) mx.at("mask").integer("size", 0) : 0;
+    if (L.window < 0) throw std::runtime_error("config: mask.size must not be negative");
+    const int nq = H * 2 * D, nk = G * 2 * D, nv = G * V, C = nq + nk + nv;
+    std::vector<float> W = sf.read_f32(p + "q", {nq, E}), b = sf.read_f32(p + "q.b", {nq}), wc;
+    append(W, sf.read_f32(p + "k", {nk, E})); append(b, sf.read_f32(p + "k.b", {nk}));
+    append(W, sf.read_f32(p + "v", {nv, E})); append(b, sf.read_f32(p + "v.b", {nv}));
+    L.proj = up_mat(m, W, C, E, &b);
+    if (taps > 0) {
+        wc = sf.read_f32(p + "q.conv", {nq, taps});
+        append(wc, sf.read_f32(p + "k.conv", {nk, taps}));
+        append(wc, sf.read_f32(p + "v.conv", {nv, taps}));
+    } else {
+        wc.assign((size_t) C, 1.f);                                       // no convolution: one unit tap (the pass that moves keys and values into the cache)
+        L.taps = 1;
+    }
+    L.wconv = up_f32(m, wc);
+    const std::vector<float> lq1 = sf.read_f32(p + "lq1", {D}), lk1 = sf.read_f32(p + "lk1", {D}), lq2 = sf.read_f32(p + "lq2", {D}), lk2 = sf.read_f32(p + "lk2", {D});
+    float d1 = 0.f, d2 = 0.f;                                             // one number per layer, float32 like everything around the scores
+    for (int i = 0; i < D; i++) { d1 = std::fmaf(lq1[(size_t) i], lk1[(size_t) i], d1); d2 = std::fmaf(lq2[(size_t) i], lk2[(size_t) i], d2); }
+    L.lambda = std::exp(d1) - std::exp(d2) + L.diff;
+    L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
+    L.n_rec = (size_t) (L.taps - 1) * C;
+    L.cache_row = (size_t) nk + nv;
+    m.maxP = std::max(m.maxP, C); m.maxA = std::max(m.maxA, H * V);
+    m.maxCV = std::max(m.maxCV, nq);
+}
+
 struct MixerEntry { const char * name; int kind; void (*load)(StackModel &, LayerSpec &, const Json &, const safetensors_file &, const std::string &); };
 const MixerEntry MIXERS[] = {
     { "mingru", MIX_MINGRU, load_mingru },
     { "latent_attention", MIX_LATENT, load_latent },
     { "delta", MIX_DELTA, load_delta },
+    { "general_delta", MIX_GDELTA, load_gdelta },
+    { "attention", MIX_DIFFATTN, load_diffattn },
 };
+
+const MixerEntry & find_mixer(const std::string & type, size_t layer) {
+    for (const MixerEntry & e : MIXERS) if (type == e.name) return e;
+    throw std::runtime_error("config: layer " + std::to_string(layer) + " has unknown mixer type '" + type + "'");
+}
+
+// one run of `layer`: its slice of the recurrent slab and, for attention, a cache of its own
+void add_run(StackModel & m, int layer, int pass) {
+    const LayerSpec & L = m.layers[(size_t) layer];
+    RunSpec r;
+    r.layer = layer; r.pass = pass;
+    r.off_rec = m.rec_floats;
+    m.rec_floats += (L.n_rec + 3) / 4 * 4;
+    if (L.cache_row) r.cache_index = m.n_caches++;
+    m.weight_bytes += L.bytes;
+    m.runs.push_back(r);
+}
 
 // ---- designs ----------------------------------------------------------------------------------------------------------
 // Matulorn: embed -> layers (x += norm1b(mixer(norm1 x)); x += norm2b(ff(norm2 x)) when the layer has one) -> final norm -> head
@@ -292,17 +426,15 @@ void build_matulorn(StackModel & m, const Json & cfg, const safetensors_file & s
     for (size_t i = 0; i < layers.arr.size(); i++) {
         const Json & lj = layers.arr[i];
         const std::string type = lj.string("type", ""), p = "l" + std::to_string(i) + ".";
-        const MixerEntry * me = nullptr;
-        for (const MixerEntry & e : MIXERS) if (type == e.name) me = &e;
-        if (!me) throw std::runtime_error("config: layer " + std::to_string(i) + " has unknown mixer type '" + type + "'");
+        const MixerEntry * me = &find_mixer(type, i);
+        if (me->kind != MIX_MINGRU && me->kind != MIX_LATENT && me->kind != MIX_DELTA) throw std::runtime_error("config: mixer '" + type + "' is not part of the Matulorn design");
+        const int64_t bytes0 = m.weight_bytes;
         m.layers.emplace_back();
         LayerSpec & L = m.layers.back();
         L.kind = me->kind;
         L.norm1 = up_f32(m, sf.read_f32(p + "norm1", {E}));
         L.norm1b = up_f32(m, sf.read_f32(p + "norm1b", {E}));
         me->load(m, L, lj.at("mixer"), sf, p + "mix.");
-        L.off_rec = m.rec_floats;
-        m.rec_floats += (L.n_rec + 3) / 4 * 4;
         if (lj.has("mlp")) {
             const Json & mj = lj.at("mlp");
             const std::string kind = mj.string("kind", "dense");
@@ -327,14 +459,91 @@ void build_matulorn(StackModel & m, const Json & cfg, const safetensors_file & s
             m.maxA = std::max(m.maxA, ff);
         }
         m.weight_bytes += (int64_t) E * 4 * (L.has_mlp ? 4 : 2);
+        L.bytes = m.weight_bytes - bytes0;
+        m.weight_bytes = bytes0;                       // counted per run
+        add_run(m, (int) i, -1);
     }
     m.final_norm = up_f32(m, sf.read_f32("final.norm", {E}));
+    m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
+}
+
+// Dopilorn: embed -> runs of layers (x += mixer(n1 x + conv) + ff(n2 x + conv), norms with zero-centred weights) with a
+// span of layers repeated `loop.times` times (x <- W_in [x; x0] + step[t] in front of every pass) -> final norm -> head -> soft cap
+void build_dopilorn(StackModel & m, const Json & cfg, const safetensors_file & sf) {
+    m.block = BLOCK_PARALLEL;
+    m.vocab = need_int(cfg, "vocab"); m.E = need_int(cfg, "width");
+    m.eps = (float) cfg.at("norm").number("eps");
+    m.groups = 1;
+    m.canon_taps = cfg.has("canon") ? need_int(cfg.at("canon"), "taps") : 0;
+    if (m.canon_taps > 64) throw std::runtime_error("config: canon.taps out of range");
+    m.softcap = (float) cfg.number("logit_softcap", 0.0);
+    const int E = m.E, ct = m.canon_taps;
+    const auto one_plus = [](std::vector<float> w) { for (float & v : w) v = 1.0f + v; return w; };      // zero-centred norm weights: the file holds w, the norm multiplies by 1 + w
+    {
+        DMat d = up_mat(m, sf.read_f32("embed", {m.vocab, E}), m.vocab, E, nullptr);
+        m.embed = d.w;
+        m.weight_bytes -= d.bytes;
+    }
+    const Json & layers = cfg.at("layers");
+    if (layers.kind != Json::Arr || layers.arr.empty()) throw std::runtime_error("config: 'layers' must be a non-empty list");
+    const int n = (int) layers.arr.size();
+    for (int i = 0; i < n; i++) {
+        const Json & lj = layers.arr[(size_t) i];
+        const std::string type = lj.string("type", ""), p = "l" + std::to_string(i) + ".";
+        const MixerEntry * me = &find_mixer(type, (size_t) i);
+        if (me->kind != MIX_LATENT && me->kind != MIX_GDELTA && me->kind != MIX_DIFFATTN) throw std::runtime_error("config: mixer '" + type + "' is not part of the Dopilorn design");
+        const int64_t bytes0 = m.weight_bytes;
+        m.layers.emplace_back();
+        LayerSpec & L = m.layers.back();
+        L.kind = me->kind;
+        L.has_mlp = lj.has("mlp");
+        L.norm1 = up_f32(m, one_plus(sf.read_f32(p + "norm1", {E})));
+        if (L.has_mlp) L.norm2 = up_f32(m, one_plus(sf.read_f32(p + "norm2", {E})));
+        me->load(m, L, lj.at("mixer"), sf, p + "mix.");
+        if (L.kind == MIX_LATENT && (L.R || L.sink || L.window)) throw std::runtime_error("config: the Dopilorn latent attention has no rotated part, sink or window");
+        if (ct > 0) {
+            std::vector<float> wc = sf.read_f32(p + "canon1", {E, ct});
+            if (L.has_mlp) append(wc, sf.read_f32(p + "canon2", {E, ct}));
+            L.canon = up_f32(m, wc);
+            if (ct > 1) L.n_rec += (size_t) (L.has_mlp ? 2 : 1) * (ct - 1) * E;       // behind the mixer's own state
+        }
+        if (L.has_mlp) {
+            const Json & mj = lj.at("mlp");
+            const std::string kind = mj.string("kind", "dense");
+            if (kind != "dense") throw std::runtime_error("config: feed-forward kind '" + kind + "' is not implemented (dense)");
+            const int ff = L.ff = need_int(mj, "ff");
+            L.ff_kind = FF_POLY;
+            L.gateup = up_mat(m, sf.read_f32(p + "mlp.up", {ff, E}), ff, E, nullptr);
+            L.down = up_mat(m, sf.read_f32(p + "mlp.down", {E, ff}), E, ff, nullptr);
+            L.act = up_f32(m, sf.read_f32(p + "mlp.act", {4}));
+            m.maxA = std::max(m.maxA, ff);
+        }
+        m.weight_bytes += (int64_t) E * 4 * (L.has_mlp ? 2 : 1) * (1 + ct);
+        L.bytes = m.weight_bytes - bytes0;
+        m.weight_bytes = bytes0;
+    }
+    int start = 0, stop = 0, times = 0;
+    if (cfg.has("loop")) {
+        const Json & lp = cfg.at("loop");
+        start = need_int(lp, "start", 0); stop = need_int(lp, "stop", 0); times = need_int(lp, "times", 0);
+        if (start > stop || stop > n) throw std::runtime_error("config: loop.start .. loop.stop must lie within the layers");
+        if (stop > start && times > 0) {
+            m.loop_in = up_mat(m, sf.read_f32("loop.in", {E, 2 * E}), E, 2 * E, nullptr);
+            m.weight_bytes += m.loop_in.bytes * (times - 1);
+            m.loop_step = up_f32(m, sf.read_f32("loop.step", {times, E}));
+        } else { start = stop = times = 0; }
+    }
+    for (int i = 0; i < start; i++) add_run(m, i, -1);
+    for (int t = 0; t < times; t++) for (int i = start; i < stop; i++) add_run(m, i, i == start ? t : -1);
+    for (int i = stop; i < n; i++) add_run(m, i, -1);
+    m.final_norm = up_f32(m, one_plus(sf.read_f32("final.norm", {E})));
     m.head = up_mat(m, sf.read_f32("head", {m.vocab, E}), m.vocab, E, nullptr);
 }
 
 struct DesignEntry { const char * name; void (*build)(StackModel &, const Json &, const safetensors_file &); };
 const DesignEntry DESIGNS[] = {
     { "Matulorn", build_matulorn },
+    { "Dopilorn", build_dopilorn },
 };
 
 // ---- launches ---------------------------------------------------------------------------------------------------------
@@ -412,12 +621,12 @@ void launch_delta_scan(StackCtx * c, const LayerSpec & L, int T, int C, float * 
     k_delta_scan<DMAX><<<grid, threads, 0, c->st>>>(c->CV, C, c->BG, T, L.H, L.KH, L.D, L.V, S, c->O);
 }
 
-// mixers: Hn [T][E] -> Y [T][E]
-void mixer_mingru(StackCtx * c, const LayerSpec & L, int T) {
-    linear(c, c->Hn, c->m->E, L.zxg, c->P, 3 * L.width, T);
-    k_mingru_scan<<<(L.width + 127) / 128, 128, 0, c->st>>>(c->P, T, L.width, c->rec + L.off_rec, c->A);
+// mixers: c->in [T][E] -> c->out [T][E]; R names the run's state
+void mixer_mingru(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    linear(c, c->in, c->m->E, L.zxg, c->P, 3 * L.width, T);
+    k_mingru_scan<<<(L.width + 127) / 128, 128, 0, c->st>>>(c->P, T, L.width, c->rec + R.off_rec, c->A);
     c->launches++;
-    linear(c, c->A, L.width, L.o, c->Y, c->m->E, T);
+    linear(c, c->A, L.width, L.o, c->out, c->m->E, T);
 }
 
 // launch shape of the latent attention for a pass of T tokens: queries per block, key slices, shared memory
@@ -473,15 +682,34 @@ void gemm_f32(StackCtx * c, const float * X, int ldx, long long sX, const float 
 constexpr int ATT_TQ = 16;                 // tokens per tile of the prompt attention
 constexpr size_t ATT_SCORE_BYTES = (size_t) 256 << 20;
 
-void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
-    const int E = c->m->E, H = L.H, D = L.D, R = L.R, rank = L.rank, V = L.V, W = rank + R;
-    const int ldp = H * (D + R) + W;
-    float * cache = c->caches[(size_t) L.cache_index];
-    linear(c, c->Hn, E, L.qdkv, c->P, ldp, T);
+// the latent attention's last steps: per-head values A[t][h] = W_uv,h (sum_j w_j c_j), head gates, output product
+void latent_values_out(StackCtx * c, const LayerSpec & L, int T, int ldp, int gate_off) {
+    const int H = L.H, V = L.V, rank = L.rank;
+    linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
+    if (L.head_gate) { k_head_gate<<<T, 256, 0, c->st>>>(c->A, c->P + gate_off, ldp, H, V); c->launches++; }
+    linear(c, c->A, H * V, L.o, c->out, c->m->E, T);
+}
+
+void mixer_latent(StackCtx * c, const LayerSpec & L, const RunSpec & Rn, int T) {
+    const int E = c->m->E, H = L.H, D = L.D, R = L.R, rank = L.rank, W = rank + R;
+    const int ldp = L.qdkv.N;
+    float * cache = c->caches[(size_t) Rn.cache_index];
+    linear(c, c->in, E, L.qdkv, c->P, ldp, T);
     const RopeArgs rope{L.rope_freq, L.rope_dims, L.rope_mag};
-    k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK);
-    // absorbed queries, one product per head: QK[t][h][0..rank) = W_uk,h^T q[t][h][0..D)
-    linear(c, c->P, ldp, L.ukT, c->QK, H * W, T, H, D + R, W);
+    int gate_off;
+    if (L.q_rank > 0) {
+        // P[t] = [ query latent | down-projection | head gates ]: norm of the query latent in place, q = W_uq c_q into A, cache row, absorbed queries from A
+        gate_off = L.q_rank + rank;
+        norm(c, c->P, ldp, nullptr, L.qnorm, L.q_rank, 1, c->P, ldp, T, false);
+        linear(c, c->P, ldp, L.uq, c->A, H * D, T);
+        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, 0, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, L.q_rank);
+        linear(c, c->A, H * D, L.ukT, c->QK, H * W, T, H, D, W);
+    } else {
+        gate_off = H * (D + R) + W;
+        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, H * (D + R));
+        // absorbed queries, one product per head: QK[t][h][0..rank) = W_uk,h^T q[t][h][0..D)
+        linear(c, c->P, ldp, L.ukT, c->QK, H * W, T, H, D + R, W);
+    }
     if (T >= 8) {
         // prompt portion: scores, row soft-max and weighted sum as float32 products over tiles of ATT_TQ tokens x all heads
         const int TQ = ATT_TQ, M = TQ * H, ntile = (T + TQ - 1) / TQ;
@@ -501,9 +729,8 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
             gemm_f32(c, c->att_scores, nk, (long long) M * nk, keys, 1, W, sK, c->OL + (size_t) g0 * M * rank, rank, (long long) M * rank, M, rank, nk, ng);
             c->launches++;
         }
-        linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
-        linear(c, c->A, H * V, L.o, c->Y, E, T);
         c->launches++;
+        latent_values_out(c, L, T, ldp, gate_off);
         return;
     }
     const AttnPlan ap = plan_attention(L, c->n_ctx, T, c->sm_count);
@@ -513,59 +740,181 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, int T) {
     else if (W % 4 == 0) k_latent_attn_staged<true><<<grid, 256, ap.smem, c->st>>>(aa);
     else k_latent_attn_staged<false><<<grid, 256, ap.smem, c->st>>>(aa);
     if (ap.nsplit > 1) { k_latent_combine<<<dim3((unsigned) T, (unsigned) H, (unsigned) ((rank + 63) / 64)), 256, 0, c->st>>>(aa); c->launches++; }
-    // values, one product per head: A[t][h] = W_uv,h (sum_j w_j c_j)
-    linear(c, c->OL, H * rank, L.uv, c->A, H * V, T, H, rank, V);
-    linear(c, c->A, H * V, L.o, c->Y, E, T);
     c->launches += 2;
+    latent_values_out(c, L, T, ldp, gate_off);
 }
 
-void mixer_delta(StackCtx * c, const LayerSpec & L, int T) {
+// causal convolution of a portion's rows with the history a sequence keeps (k_causal_conv), then the history moves on
+void causal_conv(StackCtx * c, ConvArgs a, int batch = 1) {
+    k_causal_conv<<<dim3((unsigned) ((a.C + 127) / 128), (unsigned) a.T, (unsigned) batch), 128, 0, c->st>>>(a);
+    c->launches++;
+    if (a.taps > 1) { k_causal_conv_hist<<<dim3((unsigned) ((a.C + 127) / 128), 1, (unsigned) batch), 128, 0, c->st>>>(a); c->launches++; }
+}
+
+void mixer_delta(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
     const int E = c->m->E, H = L.H, KH = L.KH, D = L.D, V = L.V, C = 2 * KH * D + H * V, ldp = C + 2 * H + H * V;
-    float * S = c->rec + L.off_rec, * hist = S + (size_t) H * D * V;
-    linear(c, c->Hn, E, L.proj, c->P, ldp, T);
-    k_delta_conv<<<dim3((unsigned) ((C + 127) / 128), (unsigned) T), 128, 0, c->st>>>(c->P, ldp, T, C, L.taps, L.wconv, hist, c->CV);
-    if (L.taps > 1) { k_delta_hist<<<(C + 127) / 128, 128, 0, c->st>>>(c->P, ldp, T, C, L.taps, hist); c->launches++; }
+    float * S = c->rec + R.off_rec, * hist = S + (size_t) H * D * V;
+    linear(c, c->in, E, L.proj, c->P, ldp, T);
+    causal_conv(c, ConvArgs{c->P, ldp, 0, L.wconv, 0, hist, 0, c->CV, C, 0, T, C, L.taps, 1, 0, nullptr, nullptr, 0, 0});
     k_delta_gates<<<T, 128, 0, c->st>>>(c->CV, C, c->P, ldp, H, KH, D, V, L.A_log, L.dt_bias, c->BG);
     if (D <= 32) launch_delta_scan<32>(c, L, T, C, S);
     else if (D <= 64) launch_delta_scan<64>(c, L, T, C, S);
     else if (D <= 128) launch_delta_scan<128>(c, L, T, C, S);
     else launch_delta_scan<256>(c, L, T, C, S);
-    k_delta_out<<<T, 128, 0, c->st>>>(c->O, c->P, ldp, C + 2 * H, H, V, L.dnorm, c->m->eps, c->A);
+    k_delta_out<<<T, 128, 0, c->st>>>(c->O, c->P, ldp, C + 2 * H, H, V, L.dnorm, 0, 0, c->m->eps, c->A);
+    c->launches += 3;
+    linear(c, c->A, H * V, L.o, c->out, E, T);
+}
+
+template <int DMAX>
+void launch_gdelta_scan(StackCtx * c, const LayerSpec & L, int T, int ldp, float * S) {
+    const int threads = std::min(128, (L.V + 31) / 32 * 32), HD = L.H * L.D;
+    const dim3 grid((unsigned) L.H, (unsigned) ((L.V + threads - 1) / threads));
+    k_gdelta_scan<DMAX><<<grid, threads, 0, c->st>>>(c->P, ldp, 0, HD, 2 * HD, c->CV, T, L.H, L.D, L.V, S, c->O);
+}
+
+// generalized delta rule: P[t] = [ r | k | v | gate | removal logit | decay latent ]
+void mixer_gdelta(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    const int E = c->m->E, H = L.H, D = L.D, V = L.V, HD = H * D, HV = H * V, ldp = L.proj.N, lat_off = 3 * HD + 2 * HV;
+    float * S = c->rec + R.off_rec;
+    linear(c, c->in, E, L.proj, c->P, ldp, T);
+    k_tanh_rows<<<T, 64, 0, c->st>>>(c->P + lat_off, ldp, L.lora);
+    linear(c, c->P + lat_off, ldp, L.w2, c->BG, HD, T);                    // decay logits (bias: w0)
+    k_gdelta_prep<<<T, 128, 0, c->st>>>(c->P, ldp, HD, 2 * HD + 2 * HV, c->BG, H, D, c->CV);
+    if (D <= 32) launch_gdelta_scan<32>(c, L, T, ldp, S);
+    else if (D <= 64) launch_gdelta_scan<64>(c, L, T, ldp, S);
+    else if (D <= 128) launch_gdelta_scan<128>(c, L, T, ldp, S);
+    else launch_gdelta_scan<256>(c, L, T, ldp, S);
+    k_delta_out<<<T, 128, 0, c->st>>>(c->O, c->P, ldp, 2 * HD + HV, H, V, L.dnorm, V, 1, c->m->eps, c->A);
     c->launches += 4;
-    linear(c, c->A, H * V, L.o, c->Y, E, T);
+    linear(c, c->A, HV, L.o, c->out, E, T);
 }
 
-void tap_layer(StackCtx * c, size_t li, int T) {
+size_t diffattn_smem(const LayerSpec & L, int TQ) {
+    const int VPL = L.V <= 32 ? 1 : L.V <= 64 ? 2 : L.V <= 128 ? 4 : 8;
+    return ((size_t) TQ * 2 * L.D + (size_t) 8 * (4 + 64 * VPL)) * 4;
+}
+
+// differential sliding-window attention: P[t] = [ q | k | v ] (biases included) -> convolution over time -> queries to CV, keys
+// and values to the cache row of the token's position -> attention with the difference and its norm -> output product
+void mixer_diffattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    const int E = c->m->E, H = L.H, G = L.KH, D = L.D, V = L.V, nq = H * 2 * D, row = (int) L.cache_row, C = nq + row;
+    float * cache = c->caches[(size_t) R.cache_index];
+    linear(c, c->in, E, L.proj, c->P, C, T);
+    causal_conv(c, ConvArgs{c->P, C, 0, L.wconv, 0, c->rec + R.off_rec, 0, c->CV, nq, 0, T, C, L.taps, 0, 0, &c->d_step->st, cache, row, nq});
+    const float * Q = c->CV;
+    const int ldq = nq;
+    const int TQ = T >= 8 ? 8 : T >= 4 ? 4 : T >= 2 ? 2 : 1;
+    DiffAttnArgs a{Q, ldq, cache, row, &c->d_step->st, c->A, T, H, G, D, V, L.window, L.scale, L.lambda, 1.0f - L.diff, c->m->eps, TQ,
+                   (D % 4 == 0 && row % 4 == 0 && ((uintptr_t) cache & 15) == 0) ? 1 : 0};
+    const dim3 grid((unsigned) ((T + TQ - 1) / TQ), (unsigned) H);
+    const size_t smem = diffattn_smem(L, TQ);
+    if (V <= 32) k_diff_attn<1><<<grid, 256, smem, c->st>>>(a);
+    else if (V <= 64) k_diff_attn<2><<<grid, 256, smem, c->st>>>(a);
+    else if (V <= 128) k_diff_attn<4><<<grid, 256, smem, c->st>>>(a);
+    else k_diff_attn<8><<<grid, 256, smem, c->st>>>(a);
+    c->launches++;
+    linear(c, c->A, H * V, L.o, c->out, E, T);
+}
+
+void tap_layer(StackCtx * c, size_t ri, int T) {
     const size_t E = (size_t) c->m->E, n = (size_t) T * E;
-    SCU(cudaMemcpyAsync(c->tap_data.data() + li * n, c->X, n * 4, cudaMemcpyDeviceToHost, c->st));
+    SCU(cudaMemcpyAsync(c->tap_data.data() + ri * n, c->X, n * 4, cudaMemcpyDeviceToHost, c->st));
 }
 
-// the layers over the T tokens whose header (positions, ids) is already on the device
-void enqueue_layers(StackCtx * c, int T) {
+void run_mixer(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
+    switch (L.kind) {
+        case MIX_MINGRU:   mixer_mingru(c, L, R, T); break;
+        case MIX_LATENT:   mixer_latent(c, L, R, T); break;
+        case MIX_DELTA:    mixer_delta(c, L, R, T); break;
+        case MIX_GDELTA:   mixer_gdelta(c, L, R, T); break;
+        default:           mixer_diffattn(c, L, R, T); break;
+    }
+}
+
+// sequential blocks: x += n1b(mixer(n1 x)); x += n2b(ff(n2 x))
+void enqueue_layers_sequential(StackCtx * c, int T) {
     StackModel & m = *c->m;
     const int E = m.E;
     const int nthreads = std::min(256, std::max(128, 32 * m.groups));
-    const float * w0 = m.layers[0].norm1;
+    const float * w0 = m.layers[(size_t) m.runs[0].layer].norm1;
     if (m.dtype == STACK_F32) k_embed_rows<float><<<T, nthreads, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, c->X, w0, m.groups, m.eps, c->Hn);
     else k_embed_rows<__nv_bfloat16><<<T, nthreads, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, c->X, w0, m.groups, m.eps, c->Hn);
     c->launches++;
-    for (size_t li = 0; li < m.layers.size(); li++) {
-        const LayerSpec & L = m.layers[li];
-        const float * next_in = li + 1 < m.layers.size() ? m.layers[li + 1].norm1 : nullptr;     // the final norm runs on the wanted rows only
-        switch (L.kind) {                              // Hn holds norm1(x)
-            case MIX_MINGRU: mixer_mingru(c, L, T); break;
-            case MIX_LATENT: mixer_latent(c, L, T); break;
-            default:         mixer_delta(c, L, T); break;
-        }
+    c->in = c->Hn; c->out = c->Y;
+    for (size_t ri = 0; ri < m.runs.size(); ri++) {
+        const RunSpec & R = m.runs[ri];
+        const LayerSpec & L = m.layers[(size_t) R.layer];
+        const float * next_in = ri + 1 < m.runs.size() ? m.layers[(size_t) m.runs[ri + 1].layer].norm1 : nullptr;     // the final norm runs on the wanted rows only
+        run_mixer(c, L, R, T);                         // Hn holds norm1(x)
         post_norm_add(c, L.norm1b, L.has_mlp ? L.norm2 : next_in, T);
         if (L.has_mlp) {
             linear(c, c->Hn, E, L.gateup, c->A, L.ff, T, 1, 0, 0, true, L.limit);      // clamped gated unit in the epilogue
             linear(c, c->A, L.ff, L.down, c->Y, E, T);
             post_norm_add(c, L.norm2b, next_in, T);
         }
-        if (c->taps) tap_layer(c, li, T);
+        if (c->taps) tap_layer(c, ri, T);
     }
     SCU(cudaGetLastError());
+}
+
+// parallel blocks: x += mixer(u1) + ff(u2), u_i = h_i + conv_i(h_i), h_i = n_i(x). The sum of a layer's two outputs is folded
+// into the kernel that norms the next layer's inputs (k_add_norm2) unless a pass of the repeated span begins in between.
+void enqueue_layers_parallel(StackCtx * c, int T) {
+    StackModel & m = *c->m;
+    const int E = m.E, ct = m.canon_taps;
+    const size_t plane = (size_t) c->cap * E;
+    const bool looped = m.loop_step != nullptr;
+    if (m.dtype == STACK_F32) k_embed_plain<float><<<T, 128, 0, c->st>>>((const float *) m.embed, c->d_step->tokens, E, m.vocab, c->X, looped ? c->XC + E : nullptr, 2 * E);
+    else k_embed_plain<__nv_bfloat16><<<T, 128, 0, c->st>>>((const __nv_bfloat16 *) m.embed, c->d_step->tokens, E, m.vocab, c->X, looped ? c->XC + E : nullptr, 2 * E);
+    c->launches++;
+    const float * ya = nullptr, * yb = nullptr;        // outputs of the layer before, not yet added to X
+    for (size_t ri = 0; ri < m.runs.size(); ri++) {
+        const RunSpec & R = m.runs[ri];
+        const LayerSpec & L = m.layers[(size_t) R.layer];
+        float * H1 = c->Hn, * H2 = c->Hn + plane;
+        if (R.pass >= 0) {
+            // x <- W_in [x; x0] + step[pass]: the finished x goes to the left half of XC (x0 is in the right half since the embedding)
+            k_add_norm2<<<T, 256, 0, c->st>>>(c->X, ya, yb, c->XC, 2 * E, nullptr, nullptr, nullptr, nullptr, E, m.eps);
+            c->launches++;
+            ya = yb = nullptr;
+            DMat w = m.loop_in;
+            w.bias = m.loop_step + (size_t) R.pass * E;
+            linear(c, c->XC, 2 * E, w, c->X, E, T);
+        }
+        k_add_norm2<<<T, 256, 0, c->st>>>(c->X, ya, yb, nullptr, 0, L.norm1, L.has_mlp ? L.norm2 : nullptr, H1, H2, E, m.eps);
+        c->launches++;
+        const int nsub = L.has_mlp ? 2 : 1;
+        const float * u1 = H1, * u2 = H2;
+        if (ct > 0) {
+            float * hist = c->rec + R.off_rec + (L.n_rec - (size_t) nsub * (ct - 1) * E);
+            causal_conv(c, ConvArgs{c->Hn, E, (long long) plane, L.canon, (long long) E * ct, hist, (long long) (ct - 1) * E, c->U, E, (long long) plane,
+                                    T, E, ct, 0, 1, nullptr, nullptr, 0, 0}, nsub);
+            u1 = c->U; u2 = c->U + plane;
+        }
+        c->in = u1; c->out = c->Y;
+        run_mixer(c, L, R, T);
+        ya = c->Y; yb = nullptr;
+        if (L.has_mlp) {
+            linear(c, u2, E, L.gateup, c->A, L.ff, T);
+            k_polynorm<<<T, 256, 0, c->st>>>(c->A, L.ff, L.act, m.eps);
+            c->launches++;
+            linear(c, c->A, L.ff, L.down, c->Y2, E, T);
+            yb = c->Y2;
+        }
+        if (c->taps || ri + 1 == m.runs.size()) {      // the residual stream itself is wanted now
+            k_add_norm2<<<T, 256, 0, c->st>>>(c->X, ya, yb, nullptr, 0, nullptr, nullptr, nullptr, nullptr, E, m.eps);
+            c->launches++;
+            ya = yb = nullptr;
+            if (c->taps) tap_layer(c, ri, T);
+        }
+    }
+    SCU(cudaGetLastError());
+}
+
+// the layers over the T tokens whose header (positions, ids) is already on the device
+void enqueue_layers(StackCtx * c, int T) {
+    if (c->m->block == BLOCK_PARALLEL) enqueue_layers_parallel(c, T); else enqueue_layers_sequential(c, T);
 }
 
 // final norm + head on n_rows rows of the pass (row indices in d_step->rows) -> d_logits[row_off ..]
@@ -573,6 +922,11 @@ void enqueue_head(StackCtx * c, int n_rows, int64_t row_off) {
     StackModel & m = *c->m;
     norm(c, c->X, m.E, c->d_step->rows, m.final_norm, m.E, m.groups, c->Hn, m.E, n_rows, false);
     linear(c, c->Hn, m.E, m.head, c->d_logits + row_off * m.vocab, m.vocab, n_rows);
+    if (m.softcap > 0.f) {
+        const size_t n = (size_t) n_rows * m.vocab;
+        k_softcap<<<(unsigned) ((n + 255) / 256), 256, 0, c->st>>>(c->d_logits + row_off * m.vocab, n, m.softcap);
+        c->launches++;
+    }
 }
 
 void ensure_logit_rows(StackCtx * c, int64_t rows) {
@@ -660,6 +1014,7 @@ void stack_ctx_free(StackCtx * c) {
     if (c->g_token) cudaGraphExecDestroy(c->g_token);
     if (c->g_greedy) cudaGraphExecDestroy(c->g_greedy);
     cudaFree(c->d_out_tokens); cudaFree(c->d_counter);
+    for (float * p : { c->Y2, c->U, c->XC }) cudaFree(p);
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
     for (float * p : c->cache_allocs) cudaFree(p);
     cudaFree(c->att_scores);
@@ -682,12 +1037,14 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         // zero-filled: rows that a tile computes beyond the portion, and cached rows no token has written, must hold finite numbers
         const auto fl = [&](float ** p, size_t n) { SCU(cudaMalloc(p, std::max<size_t>(n, 4) * 4)); SCU(cudaMemsetAsync(*p, 0, std::max<size_t>(n, 4) * 4, c->st)); };
         const size_t cap_t = (cap + ATT_TQ - 1) / ATT_TQ * ATT_TQ;
-        fl(&c->X, cap * m->E); fl(&c->Hn, cap * m->E); fl(&c->Y, cap * m->E);
+        const bool par = m->block == BLOCK_PARALLEL;
+        fl(&c->X, cap * m->E); fl(&c->Hn, cap * m->E * (par ? 2 : 1)); fl(&c->Y, cap * m->E);
+        if (par) { fl(&c->Y2, cap * m->E); fl(&c->U, cap * m->E * 2); fl(&c->XC, cap * m->E * 2); }
         fl(&c->P, cap * m->maxP); fl(&c->A, cap * m->maxA); fl(&c->QK, cap_t * m->maxQK); fl(&c->OL, cap_t * m->maxOL);
         fl(&c->CV, cap * m->maxCV); fl(&c->BG, cap * m->maxBG); fl(&c->O, cap * m->maxA);
         fl(&c->rec, m->rec_floats);
         if (m->dtype == STACK_BF16) {
-            c->xb_elems = cap * (size_t) std::max({ m->E, m->maxA, m->maxOL, m->maxP });
+            c->xb_elems = cap * (size_t) std::max({ 2 * m->E, m->maxA, m->maxOL, m->maxP });
             SCU(cudaMalloc(&c->xb, c->xb_elems * 2));
         }
         SCU(cudaMalloc(&c->d_err, 4)); SCU(cudaMemsetAsync(c->d_err, 0, 4, c->st));
@@ -697,14 +1054,22 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         SCU(cudaGetDeviceProperties(&prop, m->device));
         c->sm_count = prop.multiProcessorCount;
         size_t smem = 0, part = 0, ml = 0;
-        for (const LayerSpec & L : m->layers) {
-            if (L.kind != MIX_LATENT) continue;
+        for (const RunSpec & R : m->runs) {
+            const LayerSpec & L = m->layers[(size_t) R.layer];
+            if (R.cache_index < 0) continue;
+            if (L.kind != MIX_LATENT) {                               // one row per position, read through the window only
+                float * base = nullptr;
+                fl(&base, (size_t) n_ctx * L.cache_row);
+                c->cache_allocs.push_back(base);
+                c->caches[(size_t) R.cache_index] = base;
+                continue;
+            }
             {   // [ window - 1 zero rows | n_ctx positions | one tile of slack ]: a tile's key range may start before position 0 and end past the portion
                 const size_t front = (size_t) std::max(L.window, 1), rows = front + (size_t) n_ctx + 2 * ATT_TQ;
                 float * base = nullptr;
                 fl(&base, rows * L.cache_row);
                 c->cache_allocs.push_back(base);
-                c->caches[(size_t) L.cache_index] = base + front * L.cache_row;
+                c->caches[(size_t) R.cache_index] = base + front * L.cache_row;
                 const size_t nk = (L.window > 0 ? (size_t) L.window + ATT_TQ - 1 : (size_t) n_ctx + ATT_TQ) + 3;
                 const size_t one = (size_t) ATT_TQ * L.H * nk;             // one tile's scores
                 const size_t all = (cap_t / ATT_TQ) * one;
@@ -809,7 +1174,7 @@ void stack_decode(StackCtx * c, const int32_t * tokens, int n, int pos0, const i
         SCU(cudaStreamSynchronize(c->st));
         c->d_last_row = 0; c->h_last = c->h_logits;
     } else {
-        if (c->taps) { c->tap_data.assign(m.layers.size() * (size_t) n * m.E, 0.f); c->tap_T = n; if (n > c->cap) throw std::runtime_error("taps need a step of at most one pass"); }
+        if (c->taps) { c->tap_data.assign(m.runs.size() * (size_t) n * m.E, 0.f); c->tap_T = n; if (n > c->cap) throw std::runtime_error("taps need a step of at most one pass"); }
         int64_t row_off = 0;
         int ri = 0;
         for (int i0 = 0; i0 < n; i0 += c->cap) {

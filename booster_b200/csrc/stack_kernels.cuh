@@ -616,12 +616,14 @@ __device__ __forceinline__ void rope_pair(const RopeArgs & r, int pos, int i, fl
 // down-projection (plain weight), the last R entries are the rotated key part all heads share. The cache row of position p is
 // [ c | rotated key part ] (rank + R floats): nothing else of a key or value is kept. The query row of head h is
 // QK[t][h] = [ absorbed query (written by the per-head product q_unrotated . W_uk) | rotated query part ].
+// dkv_off: where the down-projection starts in a row of P (H (D + R) in the layout above; a design whose queries pass a
+// latent of their own keeps [ query latent | down-projection | ... ] there and has no rotated parts: R = 0).
 __global__ void k_latent_prep(const float * __restrict__ P, int ldp, int H, int D, int R, int rank, const float * __restrict__ cnorm, float eps,
-                              RopeArgs rope, const StepState * __restrict__ st, float * __restrict__ cache, float * __restrict__ QK) {
+                              RopeArgs rope, const StepState * __restrict__ st, float * __restrict__ cache, float * __restrict__ QK, int dkv_off) {
     const int t = blockIdx.x, pos = st->pos0 + t;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const float * p = P + (size_t) t * ldp;
-    const float * dkv = p + (size_t) H * (D + R);
+    const float * dkv = p + dkv_off;
     float * row = cache + (size_t) pos * (rank + R);
     const int half = rope.dims / 2;
     if (warp == 0) {
@@ -960,27 +962,49 @@ __global__ void k_latent_softmax_rows(float * __restrict__ S, int n_rows, int H,
 
 // ---- gated delta rule --------------------------------------------------------------------------------------------------
 // P[t] = [ q: KH x D | k: KH x D | v: H x V | beta logit: H | decay input: H | output-gate pre-activation: H x V ].
-// Step 1: short causal convolution over time per channel of q | k | v (taps weights, the last one the current token's, no
-// bias), then silu. hist holds the taps - 1 inputs before the portion: it is part of the sequence's state.
-__global__ void k_delta_conv(const float * __restrict__ P, int ldp, int T, int C, int taps, const float * __restrict__ wconv,
-                             const float * __restrict__ hist, float * __restrict__ CV) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
-    if (c >= C) return;
+// Step 1: short causal convolution over time per channel of q | k | v (k_causal_conv with silu), then the steps below.
+
+// ---- causal convolution over time on each channel ----------------------------------------------------------------------------
+// y_t = sum_k w[c][k] x_(t - taps + 1 + k): the last weight is the current token's, inputs before the sequence's start are zero,
+// no bias. hist holds the taps - 1 inputs before the portion ([taps - 1][C]); it is part of the sequence's state and is moved
+// on by k_causal_conv_hist after the portion. act: 0 none, 1 silu. add_input: Y = X + conv(X) (a convolution around a
+// residual path). blockIdx.z runs over a batch of independent convolutions (element strides sX / sW / sH / sY). Channels from
+// `split` on can be written to the row of the token's position in a per-position cache instead of Y (an attention's keys and
+// values after their convolution).
+struct ConvArgs {
+    const float * X; int ldx; long long sX;
+    const float * w; long long sW;
+    float * hist; long long sH;
+    float * Y; int ldy; long long sY;
+    int T, C, taps, act, add_input;
+    const StepState * st; float * cache; int ldc, split;      // cache == nullptr: everything goes to Y
+};
+__global__ void k_causal_conv(const ConvArgs a) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y, z = blockIdx.z;
+    if (c >= a.C) return;
+    const float * X = a.X + (size_t) z * a.sX;
+    const float * w = a.w + (size_t) z * a.sW + (size_t) c * a.taps;
+    const float * hist = a.hist + (size_t) z * a.sH;
     float y = 0.f;
-    for (int k = 0; k < taps; k++) {
-        const int tau = t - (taps - 1) + k;
-        const float in = tau >= 0 ? P[(size_t) tau * ldp + c] : hist[(size_t) (taps - 1 + tau) * C + c];
-        y = fmaf(wconv[(size_t) c * taps + k], in, y);
+    for (int k = 0; k < a.taps; k++) {
+        const int tau = t - (a.taps - 1) + k;
+        const float in = tau >= 0 ? X[(size_t) tau * a.ldx + c] : hist[(size_t) (a.taps - 1 + tau) * a.C + c];
+        y = fmaf(w[k], in, y);
     }
-    CV[(size_t) t * C + c] = siluf_(y);
+    if (a.add_input) y += X[(size_t) t * a.ldx + c];
+    if (a.act == 1) y = siluf_(y);
+    if (a.cache && c >= a.split) a.cache[(size_t) (a.st->pos0 + t) * a.ldc + (c - a.split)] = y;
+    else a.Y[(size_t) z * a.sY + (size_t) t * a.ldy + c] = y;
 }
 // afterwards: the history becomes the last taps - 1 inputs of (history ++ portion)
-__global__ void k_delta_hist(const float * __restrict__ P, int ldp, int T, int C, int taps, float * __restrict__ hist) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    for (int i = 0; i < taps - 1; i++) {          // ascending: entry i reads old entries at T + i > i only
-        const int f = T + i;                       // index into (history ++ portion)
-        hist[(size_t) i * C + c] = f < taps - 1 ? hist[(size_t) f * C + c] : P[(size_t) (f - (taps - 1)) * ldp + c];
+__global__ void k_causal_conv_hist(const ConvArgs a) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, z = blockIdx.z;
+    if (c >= a.C) return;
+    const float * X = a.X + (size_t) z * a.sX;
+    float * hist = a.hist + (size_t) z * a.sH;
+    for (int i = 0; i < a.taps - 1; i++) {          // ascending: entry i reads old entries at T + i > i only
+        const int f = a.T + i;                       // index into (history ++ portion)
+        hist[(size_t) i * a.C + c] = f < a.taps - 1 ? hist[(size_t) f * a.C + c] : X[(size_t) (f - (a.taps - 1)) * a.ldx + c];
     }
 }
 // Step 2, per token: q and k become unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q is also scaled by D^(-1/2);
@@ -1052,10 +1076,10 @@ __global__ void __launch_bounds__(128) k_delta_scan(const float * __restrict__ C
         for (int d = 0; d < DMAX; d++) if (d < D) Sh[(size_t) d * V + col] = s[d];
     }
 }
-// Step 4: each head's read-out over its root mean square (eps inside the root), times the shared weight [V], times
-// silu(output gate). One warp per (token, head).
+// Step 4: each head's read-out over its root mean square (eps inside the root), times a weight (w_stride 0: one [V] shared by
+// the heads; V: [H][V]), times the activated output gate (silu, or sigmoid when gate_sigmoid). One warp per (token, head).
 __global__ void k_delta_out(const float * __restrict__ O, const float * __restrict__ P, int ldp, int gate_off, int H, int V,
-                            const float * __restrict__ normw, float eps, float * __restrict__ A) {
+                            const float * __restrict__ normw, int w_stride, int gate_sigmoid, float eps, float * __restrict__ A) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     for (int h = warp; h < H; h += nw) {
         const float * o = O + (size_t) t * H * V + (size_t) h * V;
@@ -1064,8 +1088,284 @@ __global__ void k_delta_out(const float * __restrict__ O, const float * __restri
         for (int i = lane; i < V; i += 32) ss = fmaf(o[i], o[i], ss);
         ss = warp_sum(ss);
         const float r = 1.0f / sqrtf(ss / (float) V + eps);
-        for (int i = lane; i < V; i += 32) A[(size_t) t * H * V + (size_t) h * V + i] = o[i] * r * normw[i] * siluf_(gp[i]);
+        const float * nw = normw + (size_t) h * w_stride;
+        for (int i = lane; i < V; i += 32) A[(size_t) t * H * V + (size_t) h * V + i] = o[i] * r * nw[i] * (gate_sigmoid ? sigmoidf_(gp[i]) : siluf_(gp[i]));
     }
+}
+
+// ---- generalized delta rule: per-channel decay and per-channel removal along the unit key ------------------------------------
+// P[t] = [ r: H x D | k: H x D | v: H x V | output-gate pre-activation: H x V | removal logit: H x D (bias included) | ... ],
+// Wd[t] = decay logits [H x D] (the low-rank decay product, bias included). Per token and head, all in float32:
+//   w = exp(-e^(-1/2) sigmoid(decay logit))      decay of each key channel, in (e^(-e^(-1/2)), 1)
+//   u = k / sqrt(sum k^2 + 1e-6)                 unit key
+//   b = sigmoid(removal logit) * u
+// G[t][h] = [ w | u | b ] (3 D floats). One warp per (token, head).
+constexpr float GDELTA_DECAY_RATE = 0.60653065971263342f;      // e^(-1/2)
+__global__ void k_gdelta_prep(const float * __restrict__ P, int ldp, int k_off, int a_off, const float * __restrict__ Wd, int H, int D, float * __restrict__ G) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int h = warp; h < H; h += nw) {
+        const float * k = P + (size_t) t * ldp + k_off + (size_t) h * D;
+        const float * al = P + (size_t) t * ldp + a_off + (size_t) h * D;
+        const float * wl = Wd + ((size_t) t * H + h) * D;
+        float * g = G + ((size_t) t * H + h) * 3 * D;
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) ss = fmaf(k[i], k[i], ss);
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss + 1e-6f);
+        for (int i = lane; i < D; i += 32) {
+            const float u = k[i] * r;
+            g[i] = expf(-GDELTA_DECAY_RATE * sigmoidf_(wl[i]));
+            g[D + i] = u;
+            g[2 * D + i] = sigmoidf_(al[i]) * u;
+        }
+    }
+}
+// The recurrence per head; both corrections read the old state:
+//   S_t = diag(w) S_(t-1) - b (u^T S_(t-1)) + k v^T,   o_t = S_t^T r
+// S is [D][V] per head in float32. As in k_delta_scan one thread owns one column of S (D registers) and walks the portion
+// token by token: dot = sum_m u_m s_m, then s_i <- w_i s_i - b_i dot + k_i v, o = sum_i s_i r_i.
+template <int DMAX>
+__global__ void __launch_bounds__(128) k_gdelta_scan(const float * __restrict__ P, int ldp, int r_off, int k_off, int v_off, const float * __restrict__ G,
+                                                     int T, int H, int D, int V, float * __restrict__ S, float * __restrict__ O) {
+    constexpr int TT = DMAX > 128 ? 4 : 8;
+    __shared__ float rs[TT][DMAX], ks[TT][DMAX], ws[TT][DMAX], us[TT][DMAX], bs[TT][DMAX], vs[TT][128];
+    const int h = blockIdx.x, col = blockIdx.y * blockDim.x + threadIdx.x;
+    const bool live = col < V;
+    float s[DMAX];
+    float * Sh = S + (size_t) h * D * V;
+#pragma unroll
+    for (int d = 0; d < DMAX; d++) s[d] = (live && d < D) ? Sh[(size_t) d * V + col] : 0.f;
+    for (int t0 = 0; t0 < T; t0 += TT) {
+        const int nt = min(TT, T - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * DMAX; i += blockDim.x) {
+            const int tt = i / DMAX, d = i % DMAX;
+            const float * p = P + (size_t) (t0 + tt) * ldp + (size_t) h * D;
+            const float * g = G + ((size_t) (t0 + tt) * H + h) * 3 * D;
+            const bool in = d < D;
+            rs[tt][d] = in ? p[r_off + d] : 0.f;
+            ks[tt][d] = in ? p[k_off + d] : 0.f;
+            ws[tt][d] = in ? g[d] : 0.f;
+            us[tt][d] = in ? g[D + d] : 0.f;
+            bs[tt][d] = in ? g[2 * D + d] : 0.f;
+        }
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) vs[tt][threadIdx.x] = (live && tt < nt) ? P[(size_t) (t0 + tt) * ldp + v_off + (size_t) h * V + col] : 0.f;
+        __syncthreads();
+        if (!live) continue;
+        for (int tt = 0; tt < nt; tt++) {
+            const float v = vs[tt][threadIdx.x];
+            float dot = 0.f;
+#pragma unroll
+            for (int d = 0; d < DMAX; d++) dot = fmaf(us[tt][d], s[d], dot);
+            float o = 0.f;
+#pragma unroll
+            for (int d = 0; d < DMAX; d++) {
+                s[d] = fmaf(ws[tt][d], s[d], fmaf(ks[tt][d], v, -bs[tt][d] * dot));
+                o = fmaf(s[d], rs[tt][d], o);
+            }
+            O[(size_t) (t0 + tt) * H * V + (size_t) h * V + col] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int d = 0; d < DMAX; d++) if (d < D) Sh[(size_t) d * V + col] = s[d];
+    }
+}
+
+// ---- differential soft-max attention over a sliding window, grouped key/value heads -------------------------------------------
+// Every query head carries two score maps over the same values: Q[t] = [ head h: map 1 (D) | map 2 (D) ], the cached row of
+// position j is [ key head g: map 1 | map 2 (G x 2 x D) | value head g (G x V) ], query head h reads key/value head
+// h / (H / G). Position p sees j with 0 <= p - j < window (window <= 0: every j <= p). With a1, a2 the two maps' soft-max
+// averages of the values: o = a1 - lambda a2, divided by its root mean square over the V values (eps inside the root, no
+// weight), times out_scale. No positions enter the scores. Everything in float32.
+// A block takes TQ consecutive tokens of one head; the 8 / TQ warps of a query walk its keys in alternating chunks of 32 (one
+// lane per key for the scores, one lane per 32nd value channel for the weighted sum, running maximum and denominator per
+// map) and are merged through shared memory; decode (TQ = 1) so spreads one query's window over the whole block.
+struct DiffAttnArgs {
+    const float * Q; int ldq;
+    const float * cache; int ldc;
+    const StepState * st;
+    float * A;                  // [T][H x V]
+    int T, H, G, D, V, window;
+    float scale, lambda, out_scale, eps;
+    int TQ, vec;                // vec: D and ldc are multiples of 4 and the cache is 16-byte aligned
+};
+template <int VPL>
+__global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int WPQ = 8 / a.TQ, qi = warp / WPQ, wq = warp % WPQ;
+    const int h = blockIdx.y, g = h / (a.H / a.G), t0 = blockIdx.x * a.TQ, t = t0 + qi;
+    const int D2 = 2 * a.D;
+    float * qs = sm;                                        // [TQ][2 D]
+    float * mg = sm + (size_t) a.TQ * D2;                   // [8 warps][4 + 2 x 32 VPL]
+    constexpr int MGW = 4 + 64 * VPL;
+    for (int i = tid; i < a.TQ * D2; i += 256) {
+        const int q = i / D2, e = i - q * D2;
+        qs[i] = t0 + q < a.T ? a.Q[(size_t) (t0 + q) * a.ldq + (size_t) h * D2 + e] : 0.f;
+    }
+    __syncthreads();
+    float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.f, l2 = 0.f;
+    float acc1[VPL], acc2[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; i++) { acc1[i] = 0.f; acc2[i] = 0.f; }
+    if (t < a.T) {
+        const int p = a.st->pos0 + t;
+        const int jlo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+        const int nchunk = (p - jlo + 1 + 31) / 32;
+        const float * q1 = qs + (size_t) qi * D2, * q2 = q1 + a.D;
+        const size_t koff = (size_t) g * D2, voff = (size_t) a.G * D2 + (size_t) g * a.V;
+        for (int c = wq; c < nchunk; c += WPQ) {
+            const int jb = jlo + c * 32, j = jb + lane, cnt = min(32, p - jb + 1);
+            float s1 = -INFINITY, s2 = -INFINITY;
+            if (lane < cnt) {
+                const float * k1 = a.cache + (size_t) j * a.ldc + koff, * k2 = k1 + a.D;
+                float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
+                if (a.vec) {
+                    for (int e = 0; e < a.D; e += 4) {
+                        const float4 ka = __ldg(reinterpret_cast<const float4 *>(k1 + e)), kb = __ldg(reinterpret_cast<const float4 *>(k2 + e));
+                        const float4 qa = *reinterpret_cast<const float4 *>(q1 + e), qb = *reinterpret_cast<const float4 *>(q2 + e);
+                        x0 = fmaf(qa.x, ka.x, x0); x1 = fmaf(qa.y, ka.y, x1); x0 = fmaf(qa.z, ka.z, x0); x1 = fmaf(qa.w, ka.w, x1);
+                        y0 = fmaf(qb.x, kb.x, y0); y1 = fmaf(qb.y, kb.y, y1); y0 = fmaf(qb.z, kb.z, y0); y1 = fmaf(qb.w, kb.w, y1);
+                    }
+                } else {
+                    for (int e = 0; e < a.D; e++) { x0 = fmaf(q1[e], k1[e], x0); y0 = fmaf(q2[e], k2[e], y0); }
+                }
+                s1 = (x0 + x1) * a.scale; s2 = (y0 + y1) * a.scale;
+            }
+            const float n1 = fmaxf(m1, warp_max(s1)), n2 = fmaxf(m2, warp_max(s2));      // finite: the chunk holds at least one key
+            const float c1 = expf(m1 - n1), c2 = expf(m2 - n2);
+            const float e1 = lane < cnt ? expf(s1 - n1) : 0.f, e2 = lane < cnt ? expf(s2 - n2) : 0.f;
+            l1 = l1 * c1 + warp_sum(e1); l2 = l2 * c2 + warp_sum(e2);
+            m1 = n1; m2 = n2;
+#pragma unroll
+            for (int i = 0; i < VPL; i++) { acc1[i] *= c1; acc2[i] *= c2; }
+            const float * vrow = a.cache + (size_t) jb * a.ldc + voff;
+            for (int kk = 0; kk < cnt; kk++) {
+                const float w1 = __shfl_sync(0xffffffffu, e1, kk), w2 = __shfl_sync(0xffffffffu, e2, kk);
+#pragma unroll
+                for (int i = 0; i < VPL; i++) {
+                    const int vi = lane + 32 * i;
+                    const float v = vi < a.V ? __ldg(vrow + (size_t) kk * a.ldc + vi) : 0.f;
+                    acc1[i] = fmaf(w1, v, acc1[i]); acc2[i] = fmaf(w2, v, acc2[i]);
+                }
+            }
+        }
+    }
+    {
+        float * o = mg + (size_t) warp * MGW;
+        if (lane == 0) { o[0] = m1; o[1] = l1; o[2] = m2; o[3] = l2; }
+#pragma unroll
+        for (int i = 0; i < VPL; i++) { o[4 + lane + 32 * i] = acc1[i]; o[4 + 32 * VPL + lane + 32 * i] = acc2[i]; }
+    }
+    __syncthreads();
+    if (wq != 0 || t >= a.T) return;
+    // merge of the query's warps (a warp that had no chunk left m = -inf, l = 0), then the difference and its norm
+    float M1 = -INFINITY, M2 = -INFINITY;
+    for (int w = 0; w < WPQ; w++) { const float * o = mg + (size_t) (warp + w) * MGW; M1 = fmaxf(M1, o[0]); M2 = fmaxf(M2, o[2]); }
+    float L1 = 0.f, L2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) { acc1[i] = 0.f; acc2[i] = 0.f; }
+    for (int w = 0; w < WPQ; w++) {
+        const float * o = mg + (size_t) (warp + w) * MGW;
+        const float f1 = o[0] == -INFINITY ? 0.f : expf(o[0] - M1), f2 = o[2] == -INFINITY ? 0.f : expf(o[2] - M2);
+        L1 = fmaf(o[1], f1, L1); L2 = fmaf(o[3], f2, L2);
+#pragma unroll
+        for (int i = 0; i < VPL; i++) { acc1[i] = fmaf(o[4 + lane + 32 * i], f1, acc1[i]); acc2[i] = fmaf(o[4 + 32 * VPL + lane + 32 * i], f2, acc2[i]); }
+    }
+    const float i1 = 1.0f / L1, i2 = a.lambda / L2;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+        const float d = lane + 32 * i < a.V ? acc1[i] * i1 - acc2[i] * i2 : 0.f;
+        acc1[i] = d; ss = fmaf(d, d, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = a.out_scale / sqrtf(ss / (float) a.V + a.eps);
+#pragma unroll
+    for (int i = 0; i < VPL; i++) if (lane + 32 * i < a.V) a.A[(size_t) t * a.H * a.V + (size_t) h * a.V + lane + 32 * i] = acc1[i] * r;
+}
+
+// ---- blocks whose two sub-layers read the same residual: x <- x + mixer(n1(x)) + ff(n2(x)) -----------------------------------
+// End of one layer and start of the next in one pass over a row: X[t] += Ya[t] + Yb[t] (either may be absent), the new row also
+// goes to Xc (row stride ldc; the input of a product that follows) when given, then H1[t] = X^ w1 and H2[t] = X^ w2 with
+// X^ = X / sqrt(mean(X^2) + eps): both norms share the root mean square, the weights arrive as 1 + w. One block per row.
+__global__ void __launch_bounds__(256) k_add_norm2(float * __restrict__ X, const float * __restrict__ Ya, const float * __restrict__ Yb, float * __restrict__ Xc, int ldc,
+                                                   const float * __restrict__ w1, const float * __restrict__ w2, float * __restrict__ H1, float * __restrict__ H2, int n, float eps) {
+    __shared__ float red[8];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    float * x = X + (size_t) row * n;
+    float ss = 0.f;
+    for (int i = tid; i < n; i += 256) {
+        float v = x[i];
+        if (Ya) v += Ya[(size_t) row * n + i];
+        if (Yb) v += Yb[(size_t) row * n + i];
+        if (Ya || Yb) x[i] = v;
+        if (Xc) Xc[(size_t) row * ldc + i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!w1) return;
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot += red[w];
+    const float r = 1.0f / sqrtf(tot / (float) n + eps);
+    for (int i = tid; i < n; i += 256) {
+        const float v = x[i] * r;                 // each thread re-reads what it wrote
+        H1[(size_t) row * n + i] = v * w1[i];
+        if (w2) H2[(size_t) row * n + i] = v * w2[i];
+    }
+}
+
+// embedding without a norm: X[t] = embed[token[t]]; X0 (row stride ld0), when given, keeps the same row for later layers
+template <typename WT>
+__global__ void k_embed_plain(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, float * __restrict__ X, float * __restrict__ X0, int ld0) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : tok >= n_vocab ? n_vocab - 1 : tok;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        const float v = wf(embed, (size_t) tok * E + i);
+        X[(size_t) t * E + i] = v;
+        if (X0) X0[(size_t) t * ld0 + i] = v;
+    }
+}
+
+// ---- polynomial activation with norms: y = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N divides a row by its
+// root mean square (eps inside the root); coef = [a, b, c, e]. One block per row, in place, float32.
+__global__ void __launch_bounds__(256) k_polynorm(float * __restrict__ Z, int n, const float * __restrict__ coef, float eps) {
+    __shared__ float red[3][8];
+    float * z = Z + (size_t) blockIdx.x * n;
+    const int tid = threadIdx.x;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = tid; i < n; i += 256) { const float v = z[i], v2 = v * v, v3 = v2 * v; s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6); }
+    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);
+    if ((tid & 31) == 0) { red[0][tid >> 5] = s2; red[1][tid >> 5] = s4; red[2][tid >> 5] = s6; }
+    __syncthreads();
+    float t2 = 0.f, t4 = 0.f, t6 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) { t2 += red[0][w]; t4 += red[1][w]; t6 += red[2][w]; }
+    const float r1 = coef[0] / sqrtf(t2 / (float) n + eps), r2 = coef[1] / sqrtf(t4 / (float) n + eps), r3 = coef[2] / sqrtf(t6 / (float) n + eps), e = coef[3];
+    for (int i = tid; i < n; i += 256) { const float v = z[i], v2 = v * v; z[i] = fmaf(v, r1, fmaf(v2, r2, fmaf(v2 * v, r3, e))); }
+}
+
+// ---- small element-wise steps ---------------------------------------------------------------------------------------------------
+// tanh in place on n columns of each row (the middle of a low-rank product)
+__global__ void k_tanh_rows(float * __restrict__ X, int ldx, int n) {
+    float * x = X + (size_t) blockIdx.x * ldx;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = tanhf(x[i]);
+}
+// per-head output gate: A[t][h][0..V) *= sigmoid(gate[t][h]) (gate rows of stride ldg)
+__global__ void k_head_gate(float * __restrict__ A, const float * __restrict__ gate, int ldg, int H, int V) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H * V; i += blockDim.x) A[(size_t) t * H * V + i] *= sigmoidf_(gate[(size_t) t * ldg + i / V]);
+}
+// soft cap on the logits: x <- cap tanh(x / cap)
+__global__ void k_softcap(float * __restrict__ x, size_t n, float cap) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
 // ---- arg-max of one row of logits (lowest index wins ties) -----------------------------------------------------------------

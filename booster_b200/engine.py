@@ -111,9 +111,10 @@ class Context:
         return out
 
     def layer_taps(self, n_tokens: int) -> np.ndarray:
-        """layer-stack models, after set_taps(True) and one step: the residual stream after every layer, [layers, tokens, width]"""
+        """layer-stack models, after set_taps(True) and one step: the residual stream after every layer run (a layer that the
+        design repeats counts each time), [layer runs, tokens, width]"""
         t = self.get_tap("l_out", -1)
-        return t.reshape(self.model.n_layer, n_tokens, self.model.n_embd)
+        return t.reshape(-1, n_tokens, self.model.n_embd)
 
     def generate_greedy(self, first_token: int, pos0: int, n_steps: int) -> np.ndarray:
         out = np.empty(n_steps, dtype=np.int32)
