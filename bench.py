@@ -226,6 +226,59 @@ STACK_SIZES = {
 }
 
 
+def time_stack_model(engine, L, stack_io, cfg, d, args, hbm, n_prompt=2048, n_gen=64):
+    """prefill of n_prompt tokens in one step and device-resident greedy bursts of n_gen tokens, device time (CUDA events)"""
+    if not os.path.exists(os.path.join(d, "config.json")):
+        stack_io.synth_stack(d, cfg)
+    m = engine.Model(d, dtype="bfloat16")
+    c = engine.Context(m, n_prompt + n_gen * (args.steps + args.warmup) + 8)
+    prompt = np.random.default_rng(42).integers(0, cfg["vocab"], size=n_prompt).tolist()
+    pre = []
+    for i in range(args.warmup + args.steps):
+        c.kv_clear()
+        c.decode(prompt, 0)
+        if i >= args.warmup:
+            pre.append(c.last_device_ms())
+    pos, tok, dec = n_prompt, 1, []
+    for i in range(args.warmup + args.steps):
+        ids = c.generate_greedy(tok, pos, n_gen)
+        pos += n_gen; tok = int(ids[-1])
+        if i >= args.warmup:
+            dec.append(c.last_device_ms())
+    n0 = int(L.b200_kernel_launches(c.h))
+    c.generate_greedy(tok, pos, 1)
+    per_token = int(L.b200_kernel_launches(c.h)) - n0
+    res = {"params": stack_io.n_params(cfg), "weight_bytes_per_token": m.weight_bytes, "layers": [l["type"] for l in cfg["layers"]],
+           "layer_runs": stack_io.n_layer_runs(cfg), "prefill_tok_s": n_prompt / (np.median(pre) / 1e3), "prefill_tokens": n_prompt,
+           "prefill_weight_bytes_tok_s": m.weight_bytes * n_prompt / (np.median(pre) / 1e3),
+           "decode_tok_s": n_gen / (np.median(dec) / 1e3), "decode_n_kv": [n_prompt, pos],
+           "decode_hbm_frac": m.weight_bytes * n_gen / (np.median(dec) / 1e3) / (hbm * 1e9),
+           "kernel_launches": int(L.b200_kernel_launches(c.h)), "launches_per_token": per_token}
+    c.close(); m.close()
+    return res
+
+
+def bench_dopilorn(args):
+    """`--family stack --stack-design dopilorn`: prefill and decode throughput of the Dopilorn design (bfloat16 weights; random) at
+    sizes resembling real layers, beside the closest existing model, the Matulorn design, at equal width / ff / layers / heads /
+    vocabulary. The two read different numbers of weight bytes per token (other feed-forward, a repeated span), so the decode
+    fraction of the measured HBM bandwidth and the prefill rate in weight bytes x tokens per second are the comparable figures."""
+    from booster_b200 import _lib, engine, stack_io
+    L = _lib.lib()
+    hbm, hbm_src = peaks()
+    out = {"family": "stack", "design": "Dopilorn", "closest": "Matulorn", "dtype": "bf16", "data": "synthetic (random bfloat16 weights)", "hbm_gbs_peak": hbm,
+           "hbm_peak_source": hbm_src, "steps": args.steps, "warmup": args.warmup, "sizes": {}}
+    for name, sz in STACK_SIZES.items():
+        if args.stack_size and name != args.stack_size:
+            continue
+        res = {}
+        res["dopilorn"] = time_stack_model(engine, L, stack_io, stack_io.dopilorn_config(**sz), os.path.join(MODEL_DIR, f"dopilorn_{name}_s1234"), args, hbm)
+        res["matulorn"] = time_stack_model(engine, L, stack_io, stack_io.matulorn_config(**sz), os.path.join(MODEL_DIR, f"matulorn_{name}_s1234"), args, hbm)
+        out["sizes"][name] = res
+    print(json.dumps(out))
+    return 0
+
+
 def bench_stack(args):
     """Prefill and decode throughput of the Matulorn design (bfloat16 weights; random) at sizes resembling real layers, the
     LLaMA path (Q8_0, the closest block format in bytes per weight) at equal width / ff / layers / vocabulary beside it, and
@@ -331,9 +384,11 @@ def main():
     ap.add_argument("--family", default="llama", choices=["llama", "stack"],
                     help="stack: the layer-stack family (Matulorn design) beside the LLaMA path at equal layer sizes; the default workload is untouched")
     ap.add_argument("--stack-size", default="", choices=[""] + sorted(STACK_SIZES), help="--family stack: one size only")
+    ap.add_argument("--stack-design", default="matulorn", choices=["matulorn", "dopilorn"],
+                    help="--family stack: which design is measured (matulorn beside the LLaMA path; dopilorn beside matulorn)")
     args = ap.parse_args()
     if args.family == "stack":
-        return bench_stack(args)
+        return bench_dopilorn(args) if args.stack_design == "dopilorn" else bench_stack(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -1,4 +1,4 @@
-"""Synthetic models of the layer-stack family (config.json + model.safetensors) for benchmarks and smoke runs: random
+"""Synthetic models of the layer-stack family (Matulorn and Dopilorn designs; config.json + model.safetensors) for benchmarks and smoke runs: random
 bfloat16 weights of the right shapes, the counterpart of gguf_io.synth_llama for the GGUF path. Pure host code."""
 from __future__ import annotations
 
@@ -29,7 +29,77 @@ def matulorn_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 
     return {"architecture": "Matulorn", "layers": layers, "norm": {"eps": 1e-6, "groups": groups}, "vocab": vocab, "width": width}
 
 
+def dopilorn_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 32000, head_dim: int = 128, q_rank: int = 768, kv_rank: int = 512,
+                    window: int = 1024, kv_heads: int = 0, decay_rank: int = 64, taps: int = 3, loop=(2, 5, 2),
+                    pattern=("latent_attention", "general_delta", "attention")) -> dict:
+    """a Dopilorn configuration whose layers resemble a real model's: mixers in `pattern` order, a polynomial feed-forward on every
+    layer, layers loop[0] .. loop[1] - 1 run loop[2] times. `decay_rank` is not a key the loader reads (it takes the rank from the
+    tensor's shape); tensor_shapes() does."""
+    layers = []
+    for i in range(n_layer):
+        kind = pattern[i % len(pattern)]
+        if kind == "latent_attention":
+            mx = {"heads": heads, "dim": head_dim, "vdim": head_dim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": head_dim ** -0.5}
+        elif kind == "general_delta":
+            mx = {"heads": heads, "dim": head_dim, "decay_rank": decay_rank}
+        else:
+            mx = {"heads": heads, "kv_heads": kv_heads or max(1, heads // 4), "dim": head_dim // 2, "vdim": head_dim, "conv": 4, "diff": 0.5,
+                  "scale": (head_dim // 2) ** -0.5, "mask": {"size": window}}
+        layers.append({"type": kind, "mixer": mx, "mlp": {"ff": ff, "kind": "dense"}})
+    cfg = {"architecture": "Dopilorn", "canon": {"taps": taps}, "layers": layers, "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
+    if loop and loop[1] > loop[0] and loop[1] <= n_layer:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def n_layer_runs(cfg: dict) -> int:
+    lp = cfg.get("loop")
+    return len(cfg["layers"]) + ((lp["stop"] - lp["start"]) * (lp["times"] - 1) if lp else 0)
+
+
+def dopilorn_shapes(cfg: dict) -> Dict[str, List[int]]:
+    E, V = cfg["width"], cfg["vocab"]
+    t = {"embed": [V, E]}
+    lp, ct = cfg.get("loop"), (cfg.get("canon") or {}).get("taps", 0)
+    if lp:
+        t["loop.in"] = [E, 2 * E]; t["loop.step"] = [lp["times"], E]
+    for i, L in enumerate(cfg["layers"]):
+        p, mx = f"l{i}.", L["mixer"]
+        t[p + "norm1"] = [E]
+        if ct:
+            t[p + "canon1"] = [E, ct]
+        if L["type"] == "latent_attention":
+            H, D, Vd, qr, kr = mx["heads"], mx["dim"], mx["vdim"], mx["q_rank"], mx["kv_rank"]
+            t.update({p + "mix.dq": [qr, E], p + "mix.dq.norm": [qr], p + "mix.uq": [H * D, qr], p + "mix.dkv": [kr, E], p + "mix.dkv.norm": [kr],
+                      p + "mix.uk": [H * D, kr], p + "mix.uv": [H * Vd, kr], p + "mix.g": [H, E], p + "mix.o": [E, H * Vd]})
+        elif L["type"] == "general_delta":
+            n, r = mx["heads"] * mx["dim"], mx.get("decay_rank", 64)
+            t.update({p + "mix.r": [n, E], p + "mix.k": [n, E], p + "mix.v": [n, E], p + "mix.g": [n, E], p + "mix.a": [n, E], p + "mix.a.b": [n],
+                      p + "mix.w1": [r, E], p + "mix.w2": [n, r], p + "mix.w0": [n], p + "mix.norm": [n], p + "mix.o": [E, n]})
+        elif L["type"] == "attention":
+            H, G, D, Vd = mx["heads"], mx.get("kv_heads", mx["heads"]), mx["dim"], mx["vdim"]
+            for k, n in (("q", H * 2 * D), ("k", G * 2 * D), ("v", G * Vd)):
+                t[p + "mix." + k] = [n, E]; t[p + "mix." + k + ".b"] = [n]
+                if mx.get("conv"):
+                    t[p + "mix." + k + ".conv"] = [n, mx["conv"]]
+            for k in ("lq1", "lk1", "lq2", "lk2"):
+                t[p + "mix." + k] = [D]
+            t[p + "mix.o"] = [E, H * Vd]
+        else:
+            raise ValueError(L["type"])
+        if L.get("mlp"):
+            ff = L["mlp"]["ff"]
+            t.update({p + "norm2": [E], p + "mlp.up": [ff, E], p + "mlp.down": [E, ff], p + "mlp.act": [4]})
+            if ct:
+                t[p + "canon2"] = [E, ct]
+    t["final.norm"] = [E]
+    t["head"] = [V, E]
+    return t
+
+
 def tensor_shapes(cfg: dict) -> Dict[str, List[int]]:
+    if cfg.get("architecture") == "Dopilorn":
+        return dopilorn_shapes(cfg)
     E, V = cfg["width"], cfg["vocab"]
     t = {"embed": [V, E]}
     for i, L in enumerate(cfg["layers"]):
@@ -76,7 +146,12 @@ def synth_stack(d: str, cfg: dict, seed: int = 1234) -> str:
         f.write(hj)
         for name, shp in shapes.items():
             n = int(np.prod(shp))
-            if len(shp) == 2 and not name.endswith(".conv"):
+            zero_centred = cfg.get("architecture") == "Dopilorn" and name.rsplit(".", 1)[-1] in ("norm1", "norm2") or name == "final.norm" and cfg.get("architecture") == "Dopilorn"
+            if name.endswith("mlp.act"):
+                x = np.array([1.0, 0.5, 0.25, 0.0], np.float32)
+            elif "canon" in name or zero_centred or name == "loop.step":
+                x = 0.1 * rng.standard_normal(n, dtype=np.float32)
+            elif len(shp) == 2 and not name.endswith(".conv"):
                 x = rng.standard_normal(n, dtype=np.float32) * (1.0 / math.sqrt(shp[1]))
             elif "norm" in name:
                 x = 1.0 + 0.1 * rng.standard_normal(n, dtype=np.float32)
