@@ -149,6 +149,8 @@ struct StackCtx {
     size_t att_scores_floats = 0;
     std::vector<float *> cache_allocs;    // the caches with their zero margins (caches[] point behind the front margin)
     float * att_part = nullptr, * att_ml = nullptr;   // key-slice partials of the latent attention (decode)
+    float * da_part = nullptr;            // key-slice partials of the differential attention (few-token steps)
+    int * da_counter = nullptr;           // per (token, head): slices done
     int sm_count = 148;
     __nv_bfloat16 * xb = nullptr;         // activations of a prompt pass rounded to bfloat16 (operand of the tcgen05 product)
     size_t xb_elems = 0;
@@ -378,6 +380,7 @@ void load_diffattn(StackModel & m, LayerSpec & L, const Json & mx, const safeten
     L.cache_row = (size_t) nk + nv;
     m.maxP = std::max(m.maxP, C); m.maxA = std::max(m.maxA, H * V);
     m.maxCV = std::max(m.maxCV, nq);
+    m.maxQK = std::max(m.maxQK, nq); m.maxOL = std::max(m.maxOL, H * V);      // prompt portions: regrouped queries, per-group outputs
 }
 
 struct MixerEntry { const char * name; int kind; void (*load)(StackModel &, LayerSpec &, const Json &, const safetensors_file &, const std::string &); };
@@ -671,12 +674,13 @@ AttnPlan plan_attention(const LayerSpec & L, int n_ctx, int T, int sm_count) {
 }
 
 // float32 product on the CUDA cores with explicit operand layout (the attention's two products over cached rows)
+// A second batch level (nz2 products per first-level index, strides sX2 / sW2 / sY2) serves operands that are cut twice: tiles x heads.
 void gemm_f32(StackCtx * c, const float * X, int ldx, long long sX, const float * W, int w_kn, int ldw, long long sW, float * Y, int ldy, long long sY,
-              int M, int N, int K, int batch) {
+              int M, int N, int K, int batch, int nz2 = 1, long long sX2 = 0, long long sW2 = 0, long long sY2 = 0) {
     const auto al16 = [](const void * p) { return ((uintptr_t) p & 15) == 0; };
-    LinArgs a{X, W, nullptr, Y, M, N, K, ldx, ldy, sX, sW, sY, 0, 0, 0.f, 0.f, w_kn, ldw};
-    a.vec = K % 4 == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % 4 == 0 && al16(X) && al16(W);
-    k_gemm_simt<float><<<dim3((unsigned) ((N + 63) / 64), (unsigned) ((M + 63) / 64), (unsigned) batch), 256, 0, c->st>>>(a);
+    LinArgs a{X, W, nullptr, Y, M, N, K, ldx, ldy, sX, sW, sY, 0, 0, 0.f, 0.f, w_kn, ldw, nz2, sX2, sW2, sY2};
+    a.vec = K % 4 == 0 && ldx % 4 == 0 && sX % 4 == 0 && sW % 4 == 0 && sX2 % 4 == 0 && sW2 % 4 == 0 && ldw % 4 == 0 && al16(X) && al16(W);
+    k_gemm_simt<float><<<dim3((unsigned) ((N + 63) / 64), (unsigned) ((M + 63) / 64), (unsigned) (batch * nz2)), 256, 0, c->st>>>(a);
     c->launches++;
 }
 constexpr int ATT_TQ = 16;                 // tokens per tile of the prompt attention
@@ -746,22 +750,23 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, const RunSpec & Rn, int T) 
 
 // causal convolution of a portion's rows with the history a sequence keeps (k_causal_conv), then the history moves on
 void causal_conv(StackCtx * c, ConvArgs a, int batch = 1) {
+    a.fuse_hist = a.T == 1 ? 1 : 0;
     k_causal_conv<<<dim3((unsigned) ((a.C + 127) / 128), (unsigned) a.T, (unsigned) batch), 128, 0, c->st>>>(a);
     c->launches++;
-    if (a.taps > 1) { k_causal_conv_hist<<<dim3((unsigned) ((a.C + 127) / 128), 1, (unsigned) batch), 128, 0, c->st>>>(a); c->launches++; }
+    if (a.taps > 1 && !a.fuse_hist) { k_causal_conv_hist<<<dim3((unsigned) ((a.C + 127) / 128), 1, (unsigned) batch), 128, 0, c->st>>>(a); c->launches++; }
 }
 
 void mixer_delta(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
     const int E = c->m->E, H = L.H, KH = L.KH, D = L.D, V = L.V, C = 2 * KH * D + H * V, ldp = C + 2 * H + H * V;
     float * S = c->rec + R.off_rec, * hist = S + (size_t) H * D * V;
     linear(c, c->in, E, L.proj, c->P, ldp, T);
-    causal_conv(c, ConvArgs{c->P, ldp, 0, L.wconv, 0, hist, 0, c->CV, C, 0, T, C, L.taps, 1, 0, nullptr, nullptr, 0, 0});
+    causal_conv(c, ConvArgs{c->P, ldp, 0, L.wconv, 0, hist, 0, c->CV, C, 0, T, C, L.taps, 1, 0, nullptr, nullptr, 0, 0, 0});
     k_delta_gates<<<T, 128, 0, c->st>>>(c->CV, C, c->P, ldp, H, KH, D, V, L.A_log, L.dt_bias, c->BG);
     if (D <= 32) launch_delta_scan<32>(c, L, T, C, S);
     else if (D <= 64) launch_delta_scan<64>(c, L, T, C, S);
     else if (D <= 128) launch_delta_scan<128>(c, L, T, C, S);
     else launch_delta_scan<256>(c, L, T, C, S);
-    k_delta_out<<<T, 128, 0, c->st>>>(c->O, c->P, ldp, C + 2 * H, H, V, L.dnorm, 0, 0, c->m->eps, c->A);
+    k_delta_out<<<dim3((unsigned) T, (unsigned) ((H + 3) / 4)), 128, 0, c->st>>>(c->O, c->P, ldp, C + 2 * H, H, V, L.dnorm, 0, 0, c->m->eps, c->A);
     c->launches += 3;
     linear(c, c->A, H * V, L.o, c->out, E, T);
 }
@@ -780,16 +785,17 @@ void mixer_gdelta(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
     linear(c, c->in, E, L.proj, c->P, ldp, T);
     k_tanh_rows<<<T, 64, 0, c->st>>>(c->P + lat_off, ldp, L.lora);
     linear(c, c->P + lat_off, ldp, L.w2, c->BG, HD, T);                    // decay logits (bias: w0)
-    k_gdelta_prep<<<T, 128, 0, c->st>>>(c->P, ldp, HD, 2 * HD + 2 * HV, c->BG, H, D, c->CV);
+    k_gdelta_prep<<<dim3((unsigned) T, (unsigned) ((H + 3) / 4)), 128, 0, c->st>>>(c->P, ldp, HD, 2 * HD + 2 * HV, c->BG, H, D, c->CV);
     if (D <= 32) launch_gdelta_scan<32>(c, L, T, ldp, S);
     else if (D <= 64) launch_gdelta_scan<64>(c, L, T, ldp, S);
     else if (D <= 128) launch_gdelta_scan<128>(c, L, T, ldp, S);
     else launch_gdelta_scan<256>(c, L, T, ldp, S);
-    k_delta_out<<<T, 128, 0, c->st>>>(c->O, c->P, ldp, 2 * HD + HV, H, V, L.dnorm, V, 1, c->m->eps, c->A);
+    k_delta_out<<<dim3((unsigned) T, (unsigned) ((H + 3) / 4)), 128, 0, c->st>>>(c->O, c->P, ldp, 2 * HD + HV, H, V, L.dnorm, V, 1, c->m->eps, c->A);
     c->launches += 4;
     linear(c, c->A, HV, L.o, c->out, E, T);
 }
 
+constexpr int DIFF_MAX_SPLIT = 16;
 size_t diffattn_smem(const LayerSpec & L, int TQ) {
     const int VPL = L.V <= 32 ? 1 : L.V <= 64 ? 2 : L.V <= 128 ? 4 : 8;
     return ((size_t) TQ * 2 * L.D + (size_t) 8 * (4 + 64 * VPL)) * 4;
@@ -801,13 +807,43 @@ void mixer_diffattn(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T)
     const int E = c->m->E, H = L.H, G = L.KH, D = L.D, V = L.V, nq = H * 2 * D, row = (int) L.cache_row, C = nq + row;
     float * cache = c->caches[(size_t) R.cache_index];
     linear(c, c->in, E, L.proj, c->P, C, T);
-    causal_conv(c, ConvArgs{c->P, C, 0, L.wconv, 0, c->rec + R.off_rec, 0, c->CV, nq, 0, T, C, L.taps, 0, 0, &c->d_step->st, cache, row, nq});
+    causal_conv(c, ConvArgs{c->P, C, 0, L.wconv, 0, c->rec + R.off_rec, 0, c->CV, nq, 0, T, C, L.taps, 0, 0, &c->d_step->st, cache, row, nq, 0});
     const float * Q = c->CV;
     const int ldq = nq;
-    const int TQ = T >= 8 ? 8 : T >= 4 ? 4 : T >= 2 ? 2 : 1;
+    if (T >= 8) {
+        // prompt portion: float32 products over tiles of ATT_TQ tokens, one batch entry per (tile, key/value head, map)
+        const int TQ = ATT_TQ, Rh = H / G, M = TQ * Rh, ntile = (T + TQ - 1) / TQ, Tpad = ntile * TQ;
+        const int pos0 = c->h_step->st.pos0;
+        k_diff_q_layout<<<Tpad, 256, 0, c->st>>>(Q, ldq, T, Tpad, H, G, D, c->QK);
+        const int span = L.window > 0 ? std::min(L.window, pos0 + Tpad) : 0;
+        const int nk = ((L.window > 0 ? span + TQ - 1 : pos0 + Tpad) + 3) / 4 * 4;
+        const int per_group = (int) std::max<size_t>(1, c->att_scores_floats / ((size_t) 2 * G * M * nk));
+        for (int g0 = 0; g0 < ntile; g0 += per_group) {
+            const int ng = std::min(per_group, ntile - g0);
+            const long long jlo = L.window > 0 ? (long long) pos0 + (long long) g0 * TQ - span + 1 : 0;     // may be negative: zero margin in front of the cache
+            const float * keys = cache + jlo * row;
+            const long long sK = L.window > 0 ? (long long) TQ * row : 0;
+            const long long grp = (long long) ng * M * nk;                                               // one (head group, map) of this group of tiles
+            gemm_f32(c, c->QK + (size_t) g0 * M * D, D, (long long) M * D, keys, 0, row, sK, c->att_scores, nk, (long long) M * nk, M, nk, D, ng,
+                     2 * G, (long long) Tpad * Rh * D, D, grp);
+            const int rows = ng * M * G;
+            k_diff_softmax_rows<<<(rows + 7) / 8, 256, 0, c->st>>>(c->att_scores, ng * M, G, Rh, TQ, nk, L.window, span, &c->d_step->st, L.scale, L.lambda, g0, T);
+            gemm_f32(c, c->att_scores, nk, (long long) M * nk, keys + (size_t) G * 2 * D, 1, row, sK, c->OL + (size_t) g0 * M * V, V, (long long) M * V, M, V, nk, ng,
+                     G, 2 * grp, V, (long long) Tpad * Rh * V);
+            c->launches++;
+        }
+        k_diff_norm_out<<<dim3((unsigned) T, (unsigned) ((H + 3) / 4)), 128, 0, c->st>>>(c->OL, Tpad, H, G, V, c->m->eps, 1.0f - L.diff, c->A);
+        c->launches += 2;
+        linear(c, c->A, H * V, L.o, c->out, E, T);
+        return;
+    }
+    const int TQ = T >= 4 ? 4 : T >= 2 ? 2 : 1, WPQ = 8 / TQ;
+    // few queries: the keys of one query are spread over 8 / TQ warps and nsplit blocks until the grid fills the SMs
+    const int blocks = ((T + TQ - 1) / TQ) * H, max_keys = L.window > 0 ? std::min(L.window, c->n_ctx) : c->n_ctx;
+    const int nsplit = std::max(1, std::min({ 2 * c->sm_count / blocks, ((max_keys + 31) / 32 + WPQ - 1) / WPQ, DIFF_MAX_SPLIT }));
     DiffAttnArgs a{Q, ldq, cache, row, &c->d_step->st, c->A, T, H, G, D, V, L.window, L.scale, L.lambda, 1.0f - L.diff, c->m->eps, TQ,
-                   (D % 4 == 0 && row % 4 == 0 && ((uintptr_t) cache & 15) == 0) ? 1 : 0};
-    const dim3 grid((unsigned) ((T + TQ - 1) / TQ), (unsigned) H);
+                   (D % 4 == 0 && row % 4 == 0 && ((uintptr_t) cache & 15) == 0) ? 1 : 0, nsplit, c->da_part, c->da_counter};
+    const dim3 grid((unsigned) ((T + TQ - 1) / TQ), (unsigned) H, (unsigned) nsplit);
     const size_t smem = diffattn_smem(L, TQ);
     if (V <= 32) k_diff_attn<1><<<grid, 256, smem, c->st>>>(a);
     else if (V <= 64) k_diff_attn<2><<<grid, 256, smem, c->st>>>(a);
@@ -889,7 +925,7 @@ void enqueue_layers_parallel(StackCtx * c, int T) {
         if (ct > 0) {
             float * hist = c->rec + R.off_rec + (L.n_rec - (size_t) nsub * (ct - 1) * E);
             causal_conv(c, ConvArgs{c->Hn, E, (long long) plane, L.canon, (long long) E * ct, hist, (long long) (ct - 1) * E, c->U, E, (long long) plane,
-                                    T, E, ct, 0, 1, nullptr, nullptr, 0, 0}, nsub);
+                                    T, E, ct, 0, 1, nullptr, nullptr, 0, 0, 0}, nsub);
             u1 = c->U; u2 = c->U + plane;
         }
         c->in = u1; c->out = c->Y;
@@ -1017,7 +1053,7 @@ void stack_ctx_free(StackCtx * c) {
     for (float * p : { c->Y2, c->U, c->XC }) cudaFree(p);
     for (float * p : { c->X, c->Hn, c->Y, c->P, c->A, c->QK, c->OL, c->CV, c->BG, c->O, c->rec, c->d_logits }) cudaFree(p);
     for (float * p : c->cache_allocs) cudaFree(p);
-    cudaFree(c->att_scores);
+    cudaFree(c->att_scores); cudaFree(c->da_part); cudaFree(c->da_counter);
     cudaFree(c->xb); cudaFree(c->d_err); cudaFreeHost(c->h_err);
     cudaFree(c->d_step); cudaFree(c->d_arg); cudaFree(c->att_part); cudaFree(c->att_ml);
     cudaFreeHost(c->h_step); cudaFreeHost(c->h_logits); cudaFreeHost(c->h_arg);
@@ -1053,17 +1089,10 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         cudaDeviceProp prop;
         SCU(cudaGetDeviceProperties(&prop, m->device));
         c->sm_count = prop.multiProcessorCount;
-        size_t smem = 0, part = 0, ml = 0;
+        size_t smem = 0, part = 0, ml = 0, da_part = 0, da_cnt = 0;
         for (const RunSpec & R : m->runs) {
             const LayerSpec & L = m->layers[(size_t) R.layer];
             if (R.cache_index < 0) continue;
-            if (L.kind != MIX_LATENT) {                               // one row per position, read through the window only
-                float * base = nullptr;
-                fl(&base, (size_t) n_ctx * L.cache_row);
-                c->cache_allocs.push_back(base);
-                c->caches[(size_t) R.cache_index] = base;
-                continue;
-            }
             {   // [ window - 1 zero rows | n_ctx positions | one tile of slack ]: a tile's key range may start before position 0 and end past the portion
                 const size_t front = (size_t) std::max(L.window, 1), rows = front + (size_t) n_ctx + 2 * ATT_TQ;
                 float * base = nullptr;
@@ -1071,9 +1100,15 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
                 c->cache_allocs.push_back(base);
                 c->caches[(size_t) R.cache_index] = base + front * L.cache_row;
                 const size_t nk = (L.window > 0 ? (size_t) L.window + ATT_TQ - 1 : (size_t) n_ctx + ATT_TQ) + 3;
-                const size_t one = (size_t) ATT_TQ * L.H * nk;             // one tile's scores
+                const size_t one = (size_t) ATT_TQ * L.H * nk * (L.kind == MIX_DIFFATTN ? 2 : 1);     // one tile's scores (two maps per head)
                 const size_t all = (cap_t / ATT_TQ) * one;
                 c->att_scores_floats = std::max(c->att_scores_floats, std::min(all, std::max(one, ATT_SCORE_BYTES / 4)));
+            }
+            if (L.kind == MIX_DIFFATTN) {
+                const size_t mgw = 4 + 64 * (size_t) (L.V <= 32 ? 1 : L.V <= 64 ? 2 : L.V <= 128 ? 4 : 8);
+                da_part = std::max(da_part, (size_t) 8 * L.H * DIFF_MAX_SPLIT * mgw);
+                da_cnt = std::max(da_cnt, (size_t) 8 * L.H);
+                continue;
             }
             for (int T = 1; T <= std::min(c->cap, 7); T++) {      // the pass sizes that take the decode kernels: the buffers cover the largest plan
                 const AttnPlan ap = plan_attention(L, n_ctx, T, c->sm_count);
@@ -1084,6 +1119,7 @@ StackCtx * stack_ctx_new(StackModel * m, int n_ctx) {
         if (smem > 227 * 1024) throw std::runtime_error("latent attention: a context of " + std::to_string(n_ctx) + " positions without a window does not fit one block's shared memory; use a smaller n_ctx");
         c->attn_smem = smem;
         fl(&c->att_part, part); fl(&c->att_ml, ml);
+        if (da_part) { fl(&c->da_part, da_part); fl((float **) &c->da_counter, da_cnt); }
         if (c->att_scores_floats) fl(&c->att_scores, c->att_scores_floats);
         {   // the opt-in limit is a property of the kernel, not of a context: it only ever grows
             static size_t attr = 48 * 1024;

@@ -143,7 +143,10 @@ struct LinArgs {
     int vec;            // 1: K, ldx and all bases allow 16-byte loads
     int glu;            // 1: rows of W are interleaved (2i: gate_i, 2i + 1: up_i); the epilogue writes the clamped gated unit
     float limit, alpha; //    y_i = g sigmoid(alpha g) (u + 1), g = min(gate_i, limit), u = clamp(up_i, -limit, limit), to Y[t][i] (N / 2 wide)
-    int w_kn, ldw;      // w_kn = 1 (k_gemm_simt only): W is given [K][N] with row stride ldw (the attention's weights x cached rows)
+    int w_kn, ldw;      // k_gemm_simt only. w_kn = 1: W is given [K][N] with row stride ldw (the attention's weights x cached rows);
+                        // w_kn = 0 and ldw > 0: W is [N][K] with row stride ldw (keys inside wider cached rows)
+    int nz2 = 1;        // k_gemm_simt only: blockIdx.z = z1 * nz2 + z2, a second batch level with the strides below
+    long long sX2 = 0, sW2 = 0, sY2 = 0;
 };
 __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
     const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
@@ -242,8 +245,9 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
     __shared__ float Ws[16][64 + 4];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    const float * X = a.X + (size_t) blockIdx.z * a.sX;
-    const WT * W = reinterpret_cast<const WT *>(a.W) + (size_t) blockIdx.z * a.sW;
+    const int z1 = blockIdx.z / a.nz2, z2 = blockIdx.z - z1 * a.nz2;
+    const float * X = a.X + (size_t) z1 * a.sX + (size_t) z2 * a.sX2;
+    const WT * W = reinterpret_cast<const WT *>(a.W) + (size_t) z1 * a.sW + (size_t) z2 * a.sW2;
     const int lr = tid >> 2, lk = (tid & 3) * 4;          // this thread stages 4 consecutive k of row lr
     float acc[4][4];
 #pragma unroll
@@ -269,7 +273,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
                 if (a.w_kn) {
                     for (int i = 0; i < 4; i++) if (k0 + lk + i < a.K) v[i] = wf(W, (size_t) (k0 + lk + i) * a.ldw + n);
                 } else {
-                    const size_t o = (size_t) n * a.K + k0 + lk;
+                    const size_t o = (size_t) n * (a.ldw > 0 ? a.ldw : a.K) + k0 + lk;
                     if (sizeof(WT) == 4 && a.vec && k0 + lk + 3 < a.K) {
                         const float4 f = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(W) + o);
                         v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
@@ -292,7 +296,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const LinArgs a) {
         }
         __syncthreads();
     }
-    float * Y = a.Y + (size_t) blockIdx.z * a.sY;
+    float * Y = a.Y + (size_t) z1 * a.sY + (size_t) z2 * a.sY2;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int m = m0 + ty * 4 + i;
@@ -978,6 +982,7 @@ struct ConvArgs {
     float * Y; int ldy; long long sY;
     int T, C, taps, act, add_input;
     const StepState * st; float * cache; int ldc, split;      // cache == nullptr: everything goes to Y
+    int fuse_hist;                                            // T == 1: the thread also moves its channel's history on (no second launch)
 };
 __global__ void k_causal_conv(const ConvArgs a) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y, z = blockIdx.z;
@@ -995,6 +1000,11 @@ __global__ void k_causal_conv(const ConvArgs a) {
     if (a.act == 1) y = siluf_(y);
     if (a.cache && c >= a.split) a.cache[(size_t) (a.st->pos0 + t) * a.ldc + (c - a.split)] = y;
     else a.Y[(size_t) z * a.sY + (size_t) t * a.ldy + c] = y;
+    if (a.fuse_hist && a.taps > 1) {                          // one token: drop the oldest input of this channel, append the new one
+        float * h = a.hist + (size_t) z * a.sH;
+        for (int i = 0; i + 2 < a.taps; i++) h[(size_t) i * a.C + c] = h[(size_t) (i + 1) * a.C + c];
+        h[(size_t) (a.taps - 2) * a.C + c] = X[c];
+    }
 }
 // afterwards: the history becomes the last taps - 1 inputs of (history ++ portion)
 __global__ void k_causal_conv_hist(const ConvArgs a) {
@@ -1081,7 +1091,7 @@ __global__ void __launch_bounds__(128) k_delta_scan(const float * __restrict__ C
 __global__ void k_delta_out(const float * __restrict__ O, const float * __restrict__ P, int ldp, int gate_off, int H, int V,
                             const float * __restrict__ normw, int w_stride, int gate_sigmoid, float eps, float * __restrict__ A) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int h = warp; h < H; h += nw) {
+    for (int h = blockIdx.y * nw + warp; h < H; h += gridDim.y * nw) {
         const float * o = O + (size_t) t * H * V + (size_t) h * V;
         const float * gp = P + (size_t) t * ldp + gate_off + (size_t) h * V;
         float ss = 0.f;
@@ -1103,7 +1113,7 @@ __global__ void k_delta_out(const float * __restrict__ O, const float * __restri
 constexpr float GDELTA_DECAY_RATE = 0.60653065971263342f;      // e^(-1/2)
 __global__ void k_gdelta_prep(const float * __restrict__ P, int ldp, int k_off, int a_off, const float * __restrict__ Wd, int H, int D, float * __restrict__ G) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int h = warp; h < H; h += nw) {
+    for (int h = blockIdx.y * nw + warp; h < H; h += gridDim.y * nw) {
         const float * k = P + (size_t) t * ldp + k_off + (size_t) h * D;
         const float * al = P + (size_t) t * ldp + a_off + (size_t) h * D;
         const float * wl = Wd + ((size_t) t * H + h) * D;
@@ -1190,6 +1200,9 @@ struct DiffAttnArgs {
     int T, H, G, D, V, window;
     float scale, lambda, out_scale, eps;
     int TQ, vec;                // vec: D and ldc are multiples of 4 and the cache is 16-byte aligned
+    int nsplit;                 // > 1: blockIdx.z takes every nsplit-th group of chunks; the block that finishes last merges
+    float * part;               // [T][H][nsplit][4 + 64 VPL] partial (maxima, denominators, sums)
+    int * counter;              // [T][H] blocks done; the merging block puts it back to 0
 };
 template <int VPL>
 __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
@@ -1216,7 +1229,7 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
         const int nchunk = (p - jlo + 1 + 31) / 32;
         const float * q1 = qs + (size_t) qi * D2, * q2 = q1 + a.D;
         const size_t koff = (size_t) g * D2, voff = (size_t) a.G * D2 + (size_t) g * a.V;
-        for (int c = wq; c < nchunk; c += WPQ) {
+        for (int c = blockIdx.z * WPQ + wq; c < nchunk; c += WPQ * a.nsplit) {
             const int jb = jlo + c * 32, j = jb + lane, cnt = min(32, p - jb + 1);
             float s1 = -INFINITY, s2 = -INFINITY;
             if (lane < cnt) {
@@ -1274,6 +1287,35 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
 #pragma unroll
         for (int i = 0; i < VPL; i++) { acc1[i] = fmaf(o[4 + lane + 32 * i], f1, acc1[i]); acc2[i] = fmaf(o[4 + 32 * VPL + lane + 32 * i], f2, acc2[i]); }
     }
+    if (a.nsplit > 1) {
+        // leave this block's share; the block that arrives last (per token and head) merges all shares the same way
+        const size_t th = (size_t) t * a.H + h;
+        float * o = a.part + (th * a.nsplit + blockIdx.z) * MGW;
+        if (lane == 0) { o[0] = M1; o[1] = L1; o[2] = M2; o[3] = L2; }
+#pragma unroll
+        for (int i = 0; i < VPL; i++) { o[4 + lane + 32 * i] = acc1[i]; o[4 + 32 * VPL + lane + 32 * i] = acc2[i]; }
+        __threadfence();
+        int done = 0;
+        if (lane == 0) done = atomicAdd(a.counter + th, 1);
+        done = __shfl_sync(0xffffffffu, done, 0);
+        if (done != a.nsplit - 1) return;
+        __threadfence();
+        if (lane == 0) a.counter[th] = 0;
+        const float * ps = a.part + th * a.nsplit * MGW;
+        M1 = -INFINITY; M2 = -INFINITY;
+        for (int z = 0; z < a.nsplit; z++) { M1 = fmaxf(M1, __ldcg(ps + (size_t) z * MGW)); M2 = fmaxf(M2, __ldcg(ps + (size_t) z * MGW + 2)); }
+        L1 = 0.f; L2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) { acc1[i] = 0.f; acc2[i] = 0.f; }
+        for (int z = 0; z < a.nsplit; z++) {
+            const float * q = ps + (size_t) z * MGW;
+            const float z1 = __ldcg(q), z2 = __ldcg(q + 2);
+            const float f1 = z1 == -INFINITY ? 0.f : expf(z1 - M1), f2 = z2 == -INFINITY ? 0.f : expf(z2 - M2);
+            L1 = fmaf(__ldcg(q + 1), f1, L1); L2 = fmaf(__ldcg(q + 3), f2, L2);
+#pragma unroll
+            for (int i = 0; i < VPL; i++) { acc1[i] = fmaf(__ldcg(q + 4 + lane + 32 * i), f1, acc1[i]); acc2[i] = fmaf(__ldcg(q + 4 + 32 * VPL + lane + 32 * i), f2, acc2[i]); }
+        }
+    }
     const float i1 = 1.0f / L1, i2 = a.lambda / L2;
     float ss = 0.f;
 #pragma unroll
@@ -1285,6 +1327,54 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
     const float r = a.out_scale / sqrtf(ss / (float) a.V + a.eps);
 #pragma unroll
     for (int i = 0; i < VPL; i++) if (lane + 32 * i < a.V) a.A[(size_t) t * a.H * a.V + (size_t) h * a.V + lane + 32 * i] = acc1[i] * r;
+}
+
+// Prompt portions compute the same attention as float32 products, like the latent attention: per tile of TQ tokens and per
+// key/value head g, S_m = Q_(g,m) K_(g,m)^T for both maps (rows: the tile's tokens x the R = H / G query heads of the group), then
+// k_diff_softmax_rows turns the pair of score rows into ONE row of weights P = softmax(S_1) - lambda softmax(S_2) (both maps
+// weigh the same values, so the difference can be taken on the weights), then O = P V_g, then k_diff_norm_out.
+// k_diff_q_layout: queries [T][H][2][D] -> Qr[g][m][Tpad][R][D] (rows of one group and map contiguous; rows past T zero)
+__global__ void k_diff_q_layout(const float * __restrict__ Q, int ldq, int T, int Tpad, int H, int G, int D, float * __restrict__ Qr) {
+    const int t = blockIdx.x, R = H / G, nq = H * 2 * D;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const int h = i / (2 * D), m = (i / D) & 1, d = i % D, g = h / R, hq = h - g * R;
+        Qr[((((size_t) g * 2 + m) * Tpad + t) * R + hq) * D + d] = t < T ? Q[(size_t) t * ldq + i] : 0.f;
+    }
+}
+// S holds, for a group of ng tiles starting at tile0, [g][m][ng TQ R rows][nk]; row (tile, token, head) sees key jlo + n with
+// jlo = pos0 + tile TQ - span + 1 (window > 0) or 0, as in k_latent_softmax_rows. The weights replace map 1's row.
+__global__ void k_diff_softmax_rows(float * __restrict__ S, int n_rows, int G, int R, int TQ, int nk, int window, int span,
+                                    const StepState * __restrict__ st, float scale, float lambda, int tile0, int T) {
+    const int lane = threadIdx.x & 31, id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (id >= n_rows * G) return;
+    const int g = id / n_rows, r = id - g * n_rows;
+    const int tile = tile0 + r / (TQ * R), t = tile * TQ + (r % (TQ * R)) / R, p = st->pos0 + t;
+    float * s1 = S + ((size_t) (2 * g) * n_rows + r) * nk;
+    const float * s2 = s1 + (size_t) n_rows * nk;
+    if (t >= T) { for (int n = lane; n < nk; n += 32) s1[n] = 0.f; return; }
+    const int jlo = window > 0 ? st->pos0 + tile * TQ - span + 1 : 0;
+    const int n_lo = max(window > 0 ? p - window + 1 : 0, 0) - jlo, n_hi = p - jlo;         // inclusive
+    float m1 = -INFINITY, m2 = -INFINITY;
+    for (int n = n_lo + lane; n <= n_hi; n += 32) { m1 = fmaxf(m1, s1[n] * scale); m2 = fmaxf(m2, s2[n] * scale); }
+    m1 = warp_max(m1); m2 = warp_max(m2);
+    float l1 = 0.f, l2 = 0.f;
+    for (int n = n_lo + lane; n <= n_hi; n += 32) { l1 += expf(s1[n] * scale - m1); l2 += expf(s2[n] * scale - m2); }
+    l1 = warp_sum(l1); l2 = warp_sum(l2);
+    const float i1 = 1.0f / l1, i2 = lambda / l2;
+    for (int n = lane; n < nk; n += 32) s1[n] = (n >= n_lo && n <= n_hi) ? expf(s1[n] * scale - m1) * i1 - expf(s2[n] * scale - m2) * i2 : 0.f;
+}
+// Or[g][Tpad][R][V] -> A[t][h][V]: each head's vector over its root mean square (eps inside the root), times out_scale
+__global__ void k_diff_norm_out(const float * __restrict__ Or, int Tpad, int H, int G, int V, float eps, float out_scale, float * __restrict__ A) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5, R = H / G;
+    for (int h = blockIdx.y * nw + warp; h < H; h += gridDim.y * nw) {
+        const int g = h / R, hq = h - g * R;
+        const float * o = Or + (((size_t) g * Tpad + t) * R + hq) * V;
+        float ss = 0.f;
+        for (int i = lane; i < V; i += 32) ss = fmaf(o[i], o[i], ss);
+        ss = warp_sum(ss);
+        const float r = out_scale / sqrtf(ss / (float) V + eps);
+        for (int i = lane; i < V; i += 32) A[(size_t) t * H * V + (size_t) h * V + i] = o[i] * r;
+    }
 }
 
 // ---- blocks whose two sub-layers read the same residual: x <- x + mixer(n1(x)) + ff(n2(x)) -----------------------------------
