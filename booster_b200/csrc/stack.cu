@@ -341,7 +341,8 @@ void load_gdelta(StackModel & m, LayerSpec & L, const Json & mx, const safetenso
     L.o = up_mat(m, sf.read_f32(p + "o", {E, H * V}), E, H * V, nullptr);
     L.n_rec = (size_t) H * D * V;
     m.maxP = std::max(m.maxP, NP); m.maxA = std::max(m.maxA, H * V);
-    m.maxCV = std::max(m.maxCV, 3 * H * D); m.maxBG = std::max(m.maxBG, H * D);
+    if (lr > 8192) throw std::runtime_error("generalized delta rule: a decay latent above 8192 is not supported");
+    m.maxCV = std::max(m.maxCV, 3 * H * D);
 }
 
 // differential sliding-window attention: '<layer>.mix.{q,k,v}' with '.b' and '.conv', 'lq1','lk1','lq2','lk2', 'o'
@@ -704,13 +705,12 @@ void mixer_latent(StackCtx * c, const LayerSpec & L, const RunSpec & Rn, int T) 
     if (L.q_rank > 0) {
         // P[t] = [ query latent | down-projection | head gates ]: norm of the query latent in place, q = W_uq c_q into A, cache row, absorbed queries from A
         gate_off = L.q_rank + rank;
-        norm(c, c->P, ldp, nullptr, L.qnorm, L.q_rank, 1, c->P, ldp, T, false);
+        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, 0, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, L.q_rank, L.qnorm, L.q_rank);
         linear(c, c->P, ldp, L.uq, c->A, H * D, T);
-        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, 0, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, L.q_rank);
         linear(c, c->A, H * D, L.ukT, c->QK, H * W, T, H, D, W);
     } else {
         gate_off = H * (D + R) + W;
-        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, H * (D + R));
+        k_latent_prep<<<T, 128, 0, c->st>>>(c->P, ldp, H, D, R, rank, L.cnorm, c->m->eps, rope, &c->d_step->st, cache, c->QK, H * (D + R), nullptr, 0);
         // absorbed queries, one product per head: QK[t][h][0..rank) = W_uk,h^T q[t][h][0..D)
         linear(c, c->P, ldp, L.ukT, c->QK, H * W, T, H, D + R, W);
     }
@@ -783,15 +783,15 @@ void mixer_gdelta(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
     const int E = c->m->E, H = L.H, D = L.D, V = L.V, HD = H * D, HV = H * V, ldp = L.proj.N, lat_off = 3 * HD + 2 * HV;
     float * S = c->rec + R.off_rec;
     linear(c, c->in, E, L.proj, c->P, ldp, T);
-    k_tanh_rows<<<T, 64, 0, c->st>>>(c->P + lat_off, ldp, L.lora);
-    linear(c, c->P + lat_off, ldp, L.w2, c->BG, HD, T);                    // decay logits (bias: w0)
-    k_gdelta_prep<<<dim3((unsigned) T, (unsigned) ((H + 3) / 4)), 128, 0, c->st>>>(c->P, ldp, HD, 2 * HD + 2 * HV, c->BG, H, D, c->CV);
+    const dim3 pgrid((unsigned) T, (unsigned) H);
+    if (c->m->dtype == STACK_F32) k_gdelta_prep<float><<<pgrid, 128, (size_t) (L.lora + D) * 4, c->st>>>(c->P, ldp, HD, 2 * HD + 2 * HV, lat_off, L.lora, (const float *) L.w2.w, L.w2.bias, H, D, c->CV);
+    else k_gdelta_prep<__nv_bfloat16><<<pgrid, 128, (size_t) (L.lora + D) * 4, c->st>>>(c->P, ldp, HD, 2 * HD + 2 * HV, lat_off, L.lora, (const __nv_bfloat16 *) L.w2.w, L.w2.bias, H, D, c->CV);
     if (D <= 32) launch_gdelta_scan<32>(c, L, T, ldp, S);
     else if (D <= 64) launch_gdelta_scan<64>(c, L, T, ldp, S);
     else if (D <= 128) launch_gdelta_scan<128>(c, L, T, ldp, S);
     else launch_gdelta_scan<256>(c, L, T, ldp, S);
     k_delta_out<<<dim3((unsigned) T, (unsigned) ((H + 3) / 4)), 128, 0, c->st>>>(c->O, c->P, ldp, 2 * HD + HV, H, V, L.dnorm, V, 1, c->m->eps, c->A);
-    c->launches += 4;
+    c->launches += 3;
     linear(c, c->A, HV, L.o, c->out, E, T);
 }
 
@@ -918,12 +918,18 @@ void enqueue_layers_parallel(StackCtx * c, int T) {
             w.bias = m.loop_step + (size_t) R.pass * E;
             linear(c, c->XC, 2 * E, w, c->X, E, T);
         }
-        k_add_norm2<<<T, 256, 0, c->st>>>(c->X, ya, yb, nullptr, 0, L.norm1, L.has_mlp ? L.norm2 : nullptr, H1, H2, E, m.eps);
-        c->launches++;
         const int nsub = L.has_mlp ? 2 : 1;
         const float * u1 = H1, * u2 = H2;
-        if (ct > 0) {
-            float * hist = c->rec + R.off_rec + (L.n_rec - (size_t) nsub * (ct - 1) * E);
+        float * hist = c->rec + R.off_rec + (L.n_rec - (size_t) nsub * std::max(ct - 1, 0) * E);
+        if (T == 1 && ct > 0) {                        // one token: sum, both norms, both input convolutions and their history in one launch
+            k_add_norm2_canon1<<<CANON1_CTAS, 256, 0, c->st>>>(c->X, ya, yb, L.norm1, L.has_mlp ? L.norm2 : nullptr, L.canon, hist, c->U, (long long) plane, E, ct, m.eps);
+            c->launches++;
+            u1 = c->U; u2 = c->U + plane;
+        } else {
+            k_add_norm2<<<T, 256, 0, c->st>>>(c->X, ya, yb, nullptr, 0, L.norm1, L.has_mlp ? L.norm2 : nullptr, H1, H2, E, m.eps);
+            c->launches++;
+        }
+        if (ct > 0 && T > 1) {
             causal_conv(c, ConvArgs{c->Hn, E, (long long) plane, L.canon, (long long) E * ct, hist, (long long) (ct - 1) * E, c->U, E, (long long) plane,
                                     T, E, ct, 0, 1, nullptr, nullptr, 0, 0, 0}, nsub);
             u1 = c->U; u2 = c->U + plane;

@@ -9,6 +9,7 @@
 // rounds its activation operand to bfloat16.
 #pragma once
 #include <cuda_bf16.h>
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -622,12 +623,15 @@ __device__ __forceinline__ void rope_pair(const RopeArgs & r, int pos, int i, fl
 // QK[t][h] = [ absorbed query (written by the per-head product q_unrotated . W_uk) | rotated query part ].
 // dkv_off: where the down-projection starts in a row of P (H (D + R) in the layout above; a design whose queries pass a
 // latent of their own keeps [ query latent | down-projection | ... ] there and has no rotated parts: R = 0).
-__global__ void k_latent_prep(const float * __restrict__ P, int ldp, int H, int D, int R, int rank, const float * __restrict__ cnorm, float eps,
-                              RopeArgs rope, const StepState * __restrict__ st, float * __restrict__ cache, float * __restrict__ QK, int dkv_off) {
+// qnorm != nullptr: the first q_rank entries of the row (the query latent) are RMS-normed in place with that weight by a warp of their own.
+__global__ void k_latent_prep(float * __restrict__ P, int ldp, int H, int D, int R, int rank, const float * __restrict__ cnorm, float eps,
+                              RopeArgs rope, const StepState * __restrict__ st, float * __restrict__ cache, float * __restrict__ QK, int dkv_off,
+                              const float * __restrict__ qnorm, int q_rank) {
     const int t = blockIdx.x, pos = st->pos0 + t;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const float * p = P + (size_t) t * ldp;
+    float * p = P + (size_t) t * ldp;
     const float * dkv = p + dkv_off;
+    if (qnorm && warp == (nw > 1 ? 1 : 0)) warp_group_norm(p, qnorm, q_rank, eps, p, lane);
     float * row = cache + (size_t) pos * (rank + R);
     const int half = rope.dims / 2;
     if (warp == 0) {
@@ -1104,30 +1108,54 @@ __global__ void k_delta_out(const float * __restrict__ O, const float * __restri
 }
 
 // ---- generalized delta rule: per-channel decay and per-channel removal along the unit key ------------------------------------
-// P[t] = [ r: H x D | k: H x D | v: H x V | output-gate pre-activation: H x V | removal logit: H x D (bias included) | ... ],
-// Wd[t] = decay logits [H x D] (the low-rank decay product, bias included). Per token and head, all in float32:
+// P[t] = [ r: H x D | k: H x D | v: H x V | output-gate pre-activation: H x V | removal logit: H x D (bias included) | decay latent ].
+// Per token and head, all in float32:
 //   w = exp(-e^(-1/2) sigmoid(decay logit))      decay of each key channel, in (e^(-e^(-1/2)), 1)
 //   u = k / sqrt(sum k^2 + 1e-6)                 unit key
 //   b = sigmoid(removal logit) * u
-// G[t][h] = [ w | u | b ] (3 D floats). One warp per (token, head).
+// G[t][h] = [ w | u | b ] (3 D floats). One block per (token, head).
 constexpr float GDELTA_DECAY_RATE = 0.60653065971263342f;      // e^(-1/2)
-__global__ void k_gdelta_prep(const float * __restrict__ P, int ldp, int k_off, int a_off, const float * __restrict__ Wd, int H, int D, float * __restrict__ G) {
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int h = blockIdx.y * nw + warp; h < H; h += gridDim.y * nw) {
-        const float * k = P + (size_t) t * ldp + k_off + (size_t) h * D;
-        const float * al = P + (size_t) t * ldp + a_off + (size_t) h * D;
-        const float * wl = Wd + ((size_t) t * H + h) * D;
-        float * g = G + ((size_t) t * H + h) * 3 * D;
-        float ss = 0.f;
-        for (int i = lane; i < D; i += 32) ss = fmaf(k[i], k[i], ss);
-        ss = warp_sum(ss);
-        const float r = 1.0f / sqrtf(ss + 1e-6f);
-        for (int i = lane; i < D; i += 32) {
-            const float u = k[i] * r;
-            g[i] = expf(-GDELTA_DECAY_RATE * sigmoidf_(wl[i]));
-            g[D + i] = u;
-            g[2 * D + i] = sigmoidf_(al[i]) * u;
+// The decay logits are a low-rank product computed here: logit = w0 + W2 tanh(latent), latent = the last `lora` entries of the
+// row (lat_off), W2 [H D][lora] in the model's storage type; the block keeps tanh(latent) in shared memory.
+template <typename WT>
+__global__ void k_gdelta_prep(const float * __restrict__ P, int ldp, int k_off, int a_off, int lat_off, int lora, const WT * __restrict__ W2, const float * __restrict__ w0,
+                              int H, int D, float * __restrict__ G) {
+    extern __shared__ float sm_prep[];
+    float * lat = sm_prep, * wl = sm_prep + lora;            // tanh(latent) [lora], decay logits of this head [D]
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < lora; i += blockDim.x) lat[i] = tanhf(P[(size_t) t * ldp + lat_off + i]);
+    __syncthreads();
+    // a warp per row of W2, lanes striding the latent (the row is read in whole lines), PREP_RB rows at a time so that their
+    // loads are in flight together
+    constexpr int PREP_RB = 8;
+    for (int i0 = warp * PREP_RB; i0 < D; i0 += nw * PREP_RB) {
+        float acc[PREP_RB];
+#pragma unroll
+        for (int q = 0; q < PREP_RB; q++) acc[q] = 0.f;
+        for (int j = lane; j < lora; j += 32) {
+            const float x = lat[j];
+#pragma unroll
+            for (int q = 0; q < PREP_RB; q++) if (i0 + q < D) acc[q] = fmaf(wf(W2, ((size_t) h * D + i0 + q) * lora + j), x, acc[q]);
         }
+#pragma unroll
+        for (int q = 0; q < PREP_RB; q++) {
+            const float v = warp_sum(acc[q]);
+            if (lane == 0 && i0 + q < D) wl[i0 + q] = v + w0[(size_t) h * D + i0 + q];
+        }
+    }
+    const float * k = P + (size_t) t * ldp + k_off + (size_t) h * D;
+    const float * al = P + (size_t) t * ldp + a_off + (size_t) h * D;
+    float * g = G + ((size_t) t * H + h) * 3 * D;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) ss = fmaf(k[i], k[i], ss);      // every warp for itself: no second barrier round
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss + 1e-6f);
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float u = k[i] * r;
+        g[i] = expf(-GDELTA_DECAY_RATE * sigmoidf_(wl[i]));
+        g[D + i] = u;
+        g[2 * D + i] = sigmoidf_(al[i]) * u;
     }
 }
 // The recurrence per head; both corrections read the old state:
@@ -1138,7 +1166,7 @@ template <int DMAX>
 __global__ void __launch_bounds__(128) k_gdelta_scan(const float * __restrict__ P, int ldp, int r_off, int k_off, int v_off, const float * __restrict__ G,
                                                      int T, int H, int D, int V, float * __restrict__ S, float * __restrict__ O) {
     constexpr int TT = DMAX > 128 ? 4 : 8;
-    __shared__ float rs[TT][DMAX], ks[TT][DMAX], ws[TT][DMAX], us[TT][DMAX], bs[TT][DMAX], vs[TT][128];
+    __shared__ __align__(16) float rs[TT][DMAX], ks[TT][DMAX], ws[TT][DMAX], us[TT][DMAX], bs[TT][DMAX], vs[TT][128];      // aligned: the unrolled walk reads them four at a time
     const int h = blockIdx.x, col = blockIdx.y * blockDim.x + threadIdx.x;
     const bool live = col < V;
     float s[DMAX];
@@ -1165,16 +1193,17 @@ __global__ void __launch_bounds__(128) k_gdelta_scan(const float * __restrict__ 
         if (!live) continue;
         for (int tt = 0; tt < nt; tt++) {
             const float v = vs[tt][threadIdx.x];
-            float dot = 0.f;
+            float dp[4] = { 0.f, 0.f, 0.f, 0.f };      // four partial sums: the chain of dependent additions is a quarter as long
 #pragma unroll
-            for (int d = 0; d < DMAX; d++) dot = fmaf(us[tt][d], s[d], dot);
-            float o = 0.f;
+            for (int d = 0; d < DMAX; d++) dp[d & 3] = fmaf(us[tt][d], s[d], dp[d & 3]);
+            const float dot = (dp[0] + dp[1]) + (dp[2] + dp[3]);
+            float op[4] = { 0.f, 0.f, 0.f, 0.f };
 #pragma unroll
             for (int d = 0; d < DMAX; d++) {
                 s[d] = fmaf(ws[tt][d], s[d], fmaf(ks[tt][d], v, -bs[tt][d] * dot));
-                o = fmaf(s[d], rs[tt][d], o);
+                op[d & 3] = fmaf(s[d], rs[tt][d], op[d & 3]);
             }
-            O[(size_t) (t0 + tt) * H * V + (size_t) h * V + col] = o;
+            O[(size_t) (t0 + tt) * H * V + (size_t) h * V + col] = (op[0] + op[1]) + (op[2] + op[3]);
         }
     }
     if (live) {
@@ -1410,6 +1439,51 @@ __global__ void __launch_bounds__(256) k_add_norm2(float * __restrict__ X, const
     }
 }
 
+// The same for a one-token step, with the causal convolutions of both normed inputs (weights cw [2][n][taps], history
+// hist [2][taps - 1][n]) in the same launch: U_i = h_i + conv_i(h_i) to U (planes of `plane` floats), the history moves on.
+// One thread-block cluster of CANON1_CTAS blocks: each block owns a slice of the row, the sum of squares is reduced across the
+// cluster through distributed shared memory, so that no block reads an entry of X another block rewrites.
+constexpr int CANON1_CTAS = 8;
+__global__ void __cluster_dims__(CANON1_CTAS, 1, 1) __launch_bounds__(256)
+k_add_norm2_canon1(float * __restrict__ X, const float * __restrict__ Ya, const float * __restrict__ Yb, const float * __restrict__ w1, const float * __restrict__ w2,
+                   const float * __restrict__ cw, float * __restrict__ hist, float * __restrict__ U, long long plane, int n, int taps, float eps) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float red[8];
+    __shared__ float part;
+    const int tid = threadIdx.x, first = (int) cluster.block_rank() * 256 + tid, step = 256 * CANON1_CTAS;
+    float ss = 0.f;
+    for (int i = first; i < n; i += step) {
+        float v = X[i];
+        if (Ya) v += Ya[i];
+        if (Yb) v += Yb[i];
+        if (Ya || Yb) X[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) { float p = 0.f; for (int w = 0; w < 8; w++) p += red[w]; part = p; }
+    cluster.sync();
+    float tot = 0.f;
+    for (int r = 0; r < CANON1_CTAS; r++) tot += *cluster.map_shared_rank(&part, r);      // the same order in every block
+    cluster.sync();                                    // no block leaves while its share may still be read
+    const float r = 1.0f / sqrtf(tot / (float) n + eps);
+    for (int i = first; i < n; i += step) {
+        const float v = X[i] * r;                      // each thread re-reads what it wrote
+        for (int z = 0; z < (w2 ? 2 : 1); z++) {
+            const float h = v * (z ? w2[i] : w1[i]);
+            const float * c = cw + ((size_t) z * n + i) * taps;
+            float * hs = hist + (size_t) z * (taps - 1) * n;
+            float y = fmaf(c[taps - 1], h, h);
+            for (int k = 0; k + 1 < taps; k++) y = fmaf(c[k], hs[(size_t) k * n + i], y);
+            U[(size_t) z * plane + i] = y;
+            for (int k = 0; k + 2 < taps; k++) hs[(size_t) k * n + i] = hs[(size_t) (k + 1) * n + i];
+            if (taps > 1) hs[(size_t) (taps - 2) * n + i] = h;
+        }
+    }
+}
+
 // embedding without a norm: X[t] = embed[token[t]]; X0 (row stride ld0), when given, keeps the same row for later layers
 template <typename WT>
 __global__ void k_embed_plain(const WT * __restrict__ embed, const int32_t * __restrict__ tokens, int E, int n_vocab, float * __restrict__ X, float * __restrict__ X0, int ld0) {
@@ -1442,11 +1516,6 @@ __global__ void __launch_bounds__(256) k_polynorm(float * __restrict__ Z, int n,
 }
 
 // ---- small element-wise steps ---------------------------------------------------------------------------------------------------
-// tanh in place on n columns of each row (the middle of a low-rank product)
-__global__ void k_tanh_rows(float * __restrict__ X, int ldx, int n) {
-    float * x = X + (size_t) blockIdx.x * ldx;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = tanhf(x[i]);
-}
 // per-head output gate: A[t][h][0..V) *= sigmoid(gate[t][h]) (gate rows of stride ldg)
 __global__ void k_head_gate(float * __restrict__ A, const float * __restrict__ gate, int ldg, int H, int V) {
     const int t = blockIdx.x;
