@@ -773,8 +773,12 @@ void mixer_delta(StackCtx * c, const LayerSpec & L, const RunSpec & R, int T) {
 
 template <int DMAX>
 void launch_gdelta_scan(StackCtx * c, const LayerSpec & L, int T, int ldp, float * S) {
-    const int threads = std::min(128, (L.V + 31) / 32 * 32), HD = L.H * L.D;
-    const dim3 grid((unsigned) L.H, (unsigned) ((L.V + threads - 1) / threads));
+    // four lanes per column of the state; a head's columns are spread over blocks of >= 16 until the grid fills the SMs (every
+    // block stages the same r, k, w, u, b of a token tile, which is little beside its share of the walk)
+    int ncols = std::min(128, (L.V + 7) / 8 * 8);
+    while (ncols > 16 && L.H * ((L.V + ncols - 1) / ncols) < c->sm_count) ncols = (ncols / 2 + 7) / 8 * 8;
+    const int threads = GD_RG * ncols, HD = L.H * L.D;
+    const dim3 grid((unsigned) L.H, (unsigned) ((L.V + ncols - 1) / ncols));
     k_gdelta_scan<DMAX><<<grid, threads, 0, c->st>>>(c->P, ldp, 0, HD, 2 * HD, c->CV, T, L.H, L.D, L.V, S, c->O);
 }
 

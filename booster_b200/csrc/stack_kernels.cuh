@@ -1160,55 +1160,81 @@ __global__ void k_gdelta_prep(const float * __restrict__ P, int ldp, int k_off, 
 }
 // The recurrence per head; both corrections read the old state:
 //   S_t = diag(w) S_(t-1) - b (u^T S_(t-1)) + k v^T,   o_t = S_t^T r
-// S is [D][V] per head in float32. As in k_delta_scan one thread owns one column of S (D registers) and walks the portion
-// token by token: dot = sum_m u_m s_m, then s_i <- w_i s_i - b_i dot + k_i v, o = sum_i s_i r_i.
+// S is [D][V] per head in float32 and stays in registers for the whole portion. Four neighbouring lanes share one column of S,
+// each holding a quarter of its rows (DMAX / 4 registers): dot = sum_m u_m s_m and o = sum_i s_i r_i are partial sums closed
+// by two shuffles, s_i <- w_i s_i - b_i dot + k_i v in between. A block of up to 512 threads (128 columns) walks the portion
+// token by token; r, k, w, u, b of a few tokens arrive in shared memory by asynchronous copies while the tokens before
+// them are walked (two buffers), each quarter of the rows padded apart so that the four lanes' 16-byte reads fall into
+// different banks.
+constexpr int GD_RG = 4, GD_PAD = 4;
+__device__ __forceinline__ void cp_async4(float * dst, const float * src, bool real) {      // real == false: the destination gets a zero
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" :: "r"((uint32_t) __cvta_generic_to_shared(dst)), "l"(src), "r"(real ? 4u : 0u) : "memory");
+}
 template <int DMAX>
-__global__ void __launch_bounds__(128) k_gdelta_scan(const float * __restrict__ P, int ldp, int r_off, int k_off, int v_off, const float * __restrict__ G,
+__global__ void __launch_bounds__(512) k_gdelta_scan(const float * __restrict__ P, int ldp, int r_off, int k_off, int v_off, const float * __restrict__ G,
                                                      int T, int H, int D, int V, float * __restrict__ S, float * __restrict__ O) {
-    constexpr int TT = DMAX > 128 ? 4 : 8;
-    __shared__ __align__(16) float rs[TT][DMAX], ks[TT][DMAX], ws[TT][DMAX], us[TT][DMAX], bs[TT][DMAX], vs[TT][128];      // aligned: the unrolled walk reads them four at a time
-    const int h = blockIdx.x, col = blockIdx.y * blockDim.x + threadIdx.x;
+    // two buffers of GD_TT tokens: asynchronous copies fill one while the other is walked
+    constexpr int TT = DMAX > 128 ? 2 : 4, DR = DMAX / GD_RG, ROW = GD_RG * (DR + GD_PAD);
+    __shared__ __align__(16) float rs[2][TT][ROW], ks[2][TT][ROW], ws[2][TT][ROW], us[2][TT][ROW], bs[2][TT][ROW], vs[2][TT][128];
+    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, rg = lane & 3, ncols = blockDim.x / GD_RG;
+    const int cl = (tid >> 5) * 8 + (lane >> 2), col = blockIdx.y * ncols + cl;     // a warp covers 8 columns x 4 quarters
     const bool live = col < V;
-    float s[DMAX];
+    const auto stage = [&](int t0, int buf) {
+        const int nt = min(TT, T - t0);
+        for (int i = tid; i < nt * DMAX; i += blockDim.x) {
+            const int tt = i / DMAX, d = i % DMAX, at = (d / DR) * (DR + GD_PAD) + d % DR;
+            const bool in = d < D;
+            const float * p = P + (size_t) (t0 + tt) * ldp + (size_t) h * D + (in ? d : 0);
+            const float * g = G + ((size_t) (t0 + tt) * H + h) * 3 * D + (in ? d : 0);
+            cp_async4(&rs[buf][tt][at], p + r_off, in);
+            cp_async4(&ks[buf][tt][at], p + k_off, in);
+            cp_async4(&ws[buf][tt][at], g, in);
+            cp_async4(&us[buf][tt][at], g + D, in);
+            cp_async4(&bs[buf][tt][at], g + 2 * D, in);
+        }
+        for (int i = tid; i < nt * ncols; i += blockDim.x) {
+            const int tt = i / ncols, c = i % ncols;
+            const bool in = blockIdx.y * ncols + c < V;
+            cp_async4(&vs[buf][tt][c], P + (size_t) (t0 + tt) * ldp + v_off + (size_t) h * V + (in ? blockIdx.y * ncols + c : 0), in);
+        }
+    };
+    stage(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    float s[DR];
     float * Sh = S + (size_t) h * D * V;
 #pragma unroll
-    for (int d = 0; d < DMAX; d++) s[d] = (live && d < D) ? Sh[(size_t) d * V + col] : 0.f;
-    for (int t0 = 0; t0 < T; t0 += TT) {
+    for (int i = 0; i < DR; i++) { const int d = rg * DR + i; s[i] = (live && d < D) ? Sh[(size_t) d * V + col] : 0.f; }
+    const int base = rg * (DR + GD_PAD);
+    for (int t0 = 0, buf = 0; t0 < T; t0 += TT, buf ^= 1) {
         const int nt = min(TT, T - t0);
+        if (t0 + TT < T) stage(t0 + TT, buf ^ 1);            // its last readers passed the barrier that closed the previous walk
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile's copies (the group before the one just committed) have landed
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * DMAX; i += blockDim.x) {
-            const int tt = i / DMAX, d = i % DMAX;
-            const float * p = P + (size_t) (t0 + tt) * ldp + (size_t) h * D;
-            const float * g = G + ((size_t) (t0 + tt) * H + h) * 3 * D;
-            const bool in = d < D;
-            rs[tt][d] = in ? p[r_off + d] : 0.f;
-            ks[tt][d] = in ? p[k_off + d] : 0.f;
-            ws[tt][d] = in ? g[d] : 0.f;
-            us[tt][d] = in ? g[D + d] : 0.f;
-            bs[tt][d] = in ? g[2 * D + d] : 0.f;
-        }
+        for (int tt = 0; tt < nt; tt++) {                    // every lane walks (the shuffles need the whole warp); dead columns hold zeros
+            const float v = vs[buf][tt][cl];
+            float dp[4] = { 0.f, 0.f, 0.f, 0.f };
 #pragma unroll
-        for (int tt = 0; tt < TT; tt++) vs[tt][threadIdx.x] = (live && tt < nt) ? P[(size_t) (t0 + tt) * ldp + v_off + (size_t) h * V + col] : 0.f;
-        __syncthreads();
-        if (!live) continue;
-        for (int tt = 0; tt < nt; tt++) {
-            const float v = vs[tt][threadIdx.x];
-            float dp[4] = { 0.f, 0.f, 0.f, 0.f };      // four partial sums: the chain of dependent additions is a quarter as long
-#pragma unroll
-            for (int d = 0; d < DMAX; d++) dp[d & 3] = fmaf(us[tt][d], s[d], dp[d & 3]);
-            const float dot = (dp[0] + dp[1]) + (dp[2] + dp[3]);
+            for (int i = 0; i < DR; i++) dp[i & 3] = fmaf(us[buf][tt][base + i], s[i], dp[i & 3]);
+            float dot = (dp[0] + dp[1]) + (dp[2] + dp[3]);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
             float op[4] = { 0.f, 0.f, 0.f, 0.f };
 #pragma unroll
-            for (int d = 0; d < DMAX; d++) {
-                s[d] = fmaf(ws[tt][d], s[d], fmaf(ks[tt][d], v, -bs[tt][d] * dot));
-                op[d & 3] = fmaf(s[d], rs[tt][d], op[d & 3]);
+            for (int i = 0; i < DR; i++) {
+                s[i] = fmaf(ws[buf][tt][base + i], s[i], fmaf(ks[buf][tt][base + i], v, -bs[buf][tt][base + i] * dot));
+                op[i & 3] = fmaf(s[i], rs[buf][tt][base + i], op[i & 3]);
             }
-            O[(size_t) (t0 + tt) * H * V + (size_t) h * V + col] = (op[0] + op[1]) + (op[2] + op[3]);
+            float o = (op[0] + op[1]) + (op[2] + op[3]);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (rg == 0 && live) O[(size_t) (t0 + tt) * H * V + (size_t) h * V + col] = o;
         }
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
-        for (int d = 0; d < DMAX; d++) if (d < D) Sh[(size_t) d * V + col] = s[d];
+        for (int i = 0; i < DR; i++) { const int d = rg * DR + i; if (d < D) Sh[(size_t) d * V + col] = s[i]; }
     }
 }
 
