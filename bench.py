@@ -228,6 +228,7 @@ STACK_SIZES = {
 
 def time_stack_model(engine, L, stack_io, cfg, d, args, hbm, n_prompt=2048, n_gen=64):
     """prefill of n_prompt tokens in one step and device-resident greedy bursts of n_gen tokens, device time (CUDA events)"""
+    d += "_%08x" % (zlib.crc32(json.dumps(cfg, sort_keys=True).encode()) & 0xffffffff)      # a changed configuration is a new folder
     if not os.path.exists(os.path.join(d, "config.json")):
         stack_io.synth_stack(d, cfg)
     m = engine.Model(d, dtype="bfloat16")

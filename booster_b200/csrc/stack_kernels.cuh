@@ -1291,7 +1291,8 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
                 const float * k1 = a.cache + (size_t) j * a.ldc + koff, * k2 = k1 + a.D;
                 float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
                 if (a.vec) {
-                    for (int e = 0; e < a.D; e += 4) {
+#pragma unroll 8
+                    for (int e = 0; e < a.D; e += 4) {                // unrolled: the loads of several steps are in flight together
                         const float4 ka = __ldg(reinterpret_cast<const float4 *>(k1 + e)), kb = __ldg(reinterpret_cast<const float4 *>(k2 + e));
                         const float4 qa = *reinterpret_cast<const float4 *>(q1 + e), qb = *reinterpret_cast<const float4 *>(q2 + e);
                         x0 = fmaf(qa.x, ka.x, x0); x1 = fmaf(qa.y, ka.y, x1); x0 = fmaf(qa.z, ka.z, x0); x1 = fmaf(qa.w, ka.w, x1);
@@ -1310,6 +1311,7 @@ __global__ void __launch_bounds__(256) k_diff_attn(const DiffAttnArgs a) {
 #pragma unroll
             for (int i = 0; i < VPL; i++) { acc1[i] *= c1; acc2[i] *= c2; }
             const float * vrow = a.cache + (size_t) jb * a.ldc + voff;
+#pragma unroll 4
             for (int kk = 0; kk < cnt; kk++) {
                 const float w1 = __shfl_sync(0xffffffffu, e1, kk), w2 = __shfl_sync(0xffffffffu, e2, kk);
 #pragma unroll

@@ -46,6 +46,8 @@ def dopilorn_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 
             mx = {"heads": heads, "kv_heads": kv_heads or max(1, heads // 4), "dim": head_dim // 2, "vdim": head_dim, "conv": 4, "diff": 0.5,
                   "scale": (head_dim // 2) ** -0.5, "mask": {"size": window}}
         layers.append({"type": kind, "mixer": mx, "mlp": {"ff": ff, "kind": "dense"}})
+    if loop and loop[1] > n_layer:                       # few layers: the span ends with the last one
+        loop = (min(loop[0], n_layer - 1), n_layer, loop[2])
     cfg = {"architecture": "Dopilorn", "canon": {"taps": taps}, "layers": layers, "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
     if loop and loop[1] > loop[0] and loop[1] <= n_layer:
         cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
