@@ -265,7 +265,7 @@ def test_long_decoding_through_the_graph(tmp_path):
     p.close()
 
 
-@pytest.mark.parametrize("width,vocab,taps", [(36, 50, 1), (40, 77, 4), (64, 130, 2)], ids=["scalar-loads-one-tap", "four-taps", "vector-loads"])
+@pytest.mark.parametrize("width,vocab,taps", [(36, 50, 1), (40, 77, 4), (64, 130, 2), (37, 53, 3)], ids=["scalar-loads-one-tap", "four-taps", "vector-loads", "odd-width"])
 def test_other_sizes(tmp_path, width, vocab, taps):
     layers = [attn(heads=6, kv_heads=2, dim=9, vdim=5, conv=1, window=4, diff=0.1, mlp=ff(20)), latent(heads=1, dim=6, vdim=3, q_rank=5, kv_rank=9),
               gdelta(heads=1, dim=64, decay_rank=3), attn(heads=4, kv_heads=4, dim=16, vdim=40, conv=5, window=50, diff=0.8),
