@@ -30,7 +30,7 @@ def matulorn_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 
 
 
 def dopilorn_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 32000, head_dim: int = 128, q_rank: int = 768, kv_rank: int = 512,
-                    window: int = 1024, kv_heads: int = 0, decay_rank: int = 64, taps: int = 3, loop=(2, 5, 2),
+                    window: int = 1024, kv_heads: int = 0, decay_rank: int = 64, taps: int = 4, loop=(2, 5, 2),
                     pattern=("latent_attention", "general_delta", "attention")) -> dict:
     """a Dopilorn configuration whose layers resemble a real model's: mixers in `pattern` order, a polynomial feed-forward on every
     layer, layers loop[0] .. loop[1] - 1 run loop[2] times. `decay_rank` is not a key the loader reads (it takes the rank from the
@@ -48,7 +48,7 @@ def dopilorn_config(width: int, n_layer: int, ff: int, heads: int, vocab: int = 
         layers.append({"type": kind, "mixer": mx, "mlp": {"ff": ff, "kind": "dense"}})
     if loop and loop[1] > n_layer:                       # few layers: the span ends with the last one
         loop = (min(loop[0], n_layer - 1), n_layer, loop[2])
-    cfg = {"architecture": "Dopilorn", "canon": {"taps": taps}, "layers": layers, "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
+    cfg = {"architecture": "Dopilorn", "canon": {"taps": taps}, "layers": layers, "logit_softcap": 50.0, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
     if loop and loop[1] > loop[0] and loop[1] <= n_layer:
         cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
     return cfg

@@ -123,11 +123,11 @@ def test_input_convolution_norm_weights_cap_and_activation_matter(tmp_path):
     p.close()
 
 
-FULL = [latent(mlp=ff()), gdelta(mlp=ff(40)), attn(mlp=ff()), latent(heads=2, dim=12, vdim=4, q_rank=6, kv_rank=16), gdelta(heads=2, dim=16),
-        attn(heads=2, kv_heads=1, dim=8, vdim=16, conv=2, window=11, mlp=ff(32))]
+FULL = [gdelta(mlp=ff(40)), latent(mlp=ff()), attn(mlp=ff()), gdelta(heads=2, dim=16), attn(heads=2, kv_heads=1, dim=8, vdim=16, conv=2, window=11, mlp=ff(32)),
+        latent(heads=2, dim=12, vdim=4, q_rank=6, kv_rank=16)]
 
 
-@pytest.mark.parametrize("loop", [None, (1, 5, 2), (0, 6, 3), (2, 3, 1), (4, 6, 2)], ids=str)
+@pytest.mark.parametrize("loop", [None, (1, 4, 2), (0, 6, 3), (2, 3, 1), (3, 6, 2)], ids=str)
 def test_whole_prompt_token_by_token_and_portions_agree(tmp_path, loop):
     p = Pair(tmp_path, config(FULL, loop=loop, taps=3))
     toks = p.tokens(75)
@@ -337,7 +337,7 @@ def row_errs(got, want):
 
 
 def test_bfloat16_prompt_kernels_and_decode(tmp_path):
-    cfg = config(FULL, width=64, vocab=96, loop=(1, 5, 2))
+    cfg = config(FULL, width=64, vocab=96, loop=(2, 5, 2))
     p = Pair(tmp_path, cfg, dtype="bfloat16")
     toks = p.tokens(150, seed=2)
     want = p.expected(toks)
