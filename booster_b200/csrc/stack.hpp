@@ -1,5 +1,6 @@
 // stack.hpp — host interface of the layer-stack model family (stack.cu): models described by a config.json whose
-// "layers" list names, per layer, a mixer (minGRU | latent attention | gated delta rule) and an optional feed-forward.
+// "layers" list names, per layer, a mixer (minGRU | latent attention | gated delta rule | generalized delta rule |
+// differential sliding-window attention) and an optional feed-forward; two designs (Matulorn, Dopilorn) arrange them.
 // engine.cu dispatches the C-ABI (b200_model_load, b200_ctx_new, b200_decode, ...) here when the model path is a folder
 // with config.json + model.safetensors; the GGUF LLaMA path stays where it was. Functions throw std::runtime_error.
 #pragma once
@@ -25,7 +26,8 @@ int          stack_model_device(const StackModel * m);
 int          stack_model_n_vocab(const StackModel * m);
 
 // One sequence per context, like the LLaMA contexts: a cache of n_ctx positions for the attention layers and the
-// recurrent state (minGRU state, delta-rule matrices, convolution history) of the other mixers, all in float32.
+// recurrent state (minGRU state, delta-rule matrices, convolution history) of the other mixers, all in float32. A layer
+// that a design runs several times per token keeps one cache / state per run.
 StackCtx * stack_ctx_new(StackModel * m, int n_ctx);
 void       stack_ctx_free(StackCtx * c);
 int        stack_ctx_n_ctx(const StackCtx * c);
@@ -42,7 +44,7 @@ void    stack_generate_greedy(StackCtx * c, int32_t first_token, int pos0, int n
 void    stack_sync(StackCtx * c);
 float * stack_logits_view(StackCtx * c);             // pinned host copy of the last computed row of logits
 int32_t stack_argmax(StackCtx * c);                  // arg-max of that row, computed on the device
-// residual stream after every layer of the LAST step, host [n_layers][n][width] (parity tests); enable before the step
+// residual stream after every layer run of the LAST step, host [n_runs][n][width] (parity tests); enable before the step
 void    stack_set_taps(StackCtx * c, bool on);
 int64_t stack_get_taps(StackCtx * c, float * out, int64_t cap);
 float   stack_last_device_ms(const StackCtx * c);

@@ -1,7 +1,9 @@
 // stack_kernels.cuh — CUDA kernels (sm_100a) of the layer-stack models: a residual stream that passes a configurable
 // list of layers, each one mixer (minGRU recurrence | latent attention with a sliding window and a soft-max sink |
-// gated delta rule) and an optional clamped gated feed-forward, with grouped RMS norms before and after every
-// sub-layer. Every size and constant is a kernel argument; nothing is specialised for one model.
+// gated delta rule | generalized delta rule | differential sliding-window attention) and an optional feed-forward
+// (clamped gated unit | polynomial activation with norms), either one sub-layer after the other with grouped RMS norms
+// before and after each, or both reading the same residual behind causal convolutions of their normed inputs.
+// Every size and constant is a kernel argument; nothing is specialised for one model.
 //
 // Precision: the residual stream, norms, positions and angles, attention scores and weights, recurrent states and
 // everything that enters a recurrence are float32. Matrix products take float32 activations and weights in the
